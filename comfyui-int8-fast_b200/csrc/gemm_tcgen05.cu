@@ -1,0 +1,603 @@
+// C[M,N] = A[M,K] * B[N,K]^T on the sm_100a tensor cores (tcgen05.mma), with
+// both operands K-major in global memory, staged by TMA into a shared-memory
+// ring, accumulated in tensor memory and drained by a fused epilogue.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0 (one lane)  TMA producer: fills ring stages, signals `full`
+//   warp 1 (one lane)  MMA issuer:   4 x tcgen05.mma per stage (32 bytes of K
+//                                    each), tcgen05.commit frees the stage
+//                                    (`empty`) and publishes a finished tile
+//                                    (`acc_full`)
+//   warps 2..5         epilogue:     tcgen05.ld the 128 x BN accumulator (one
+//                                    row per thread), dequantise / cast, store,
+//                                    then hand the TMEM buffer back (`acc_empty`)
+// The accumulator is double buffered in tensor memory (2 x BN columns) so the
+// epilogue of tile i overlaps the MMAs of tile i+1.
+//
+// Every mbarrier wait is bounded: a wait that runs out writes a code to the
+// device status word, raises a CTA-wide abort flag and all roles fall through
+// to the common teardown (which still frees the tensor memory).
+//
+// No TMA load in this file uses cluster multicast.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+
+namespace i8f {
+namespace {
+
+constexpr int kBM = 128;            // rows of A per tile == TMEM lanes
+constexpr int kStageRowBytes = 128; // one 128-byte swizzle span of K per stage
+constexpr int kThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+enum Kind : int { kKindI8 = 0, kKindBF16 = 1, kKindF16 = 2 };
+enum EpiMode : int { kEpiI32 = 0, kEpiDequant = 1, kEpiCast = 2, kEpiAccum = 3 };
+
+// status codes written by bounded waits
+enum : int { kStEmptyWait = 101, kStFullWait = 102, kStAccEmptyWait = 103, kStAccFullWait = 104 };
+
+struct GemmParams {
+    int M, N;
+    int num_k_blocks;
+    int tiles_m, tiles_n;
+    void* out;
+    long long ldo;
+    int out_dtype;
+    const float* a_scale;
+    const float* w_scale;
+    int w_scale_mode;
+    const void* bias;
+    int bias_dtype;
+    int epi_mode;
+    int epi_order;
+    int vec_ok;  // out pointer / pitch allow 16-byte row-segment stores
+    int* status;
+};
+
+template <int BN>
+struct Cfg {
+    static constexpr int kABytes = kBM * kStageRowBytes;
+    static constexpr int kBBytes = BN * kStageRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (192 * 1024) / kStageBytes;
+    static constexpr int kTmemCols = 2 * BN;  // 512, 256 or 128: powers of two >= 32
+    static constexpr int kBarrierBytes = 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
+    // groups of 8 row-blocks, row-block fastest inside a group
+    const int group_sz = 8 * tiles_n;
+    const int group = t / group_sz;
+    const int first_m = group * 8;
+    const int gm = min(tiles_m - first_m, 8);
+    const int r = t - group * group_sz;
+    m_blk = first_m + r % gm;
+    n_blk = r / gm;
+}
+
+template <int DT>
+__device__ __forceinline__ float round_out(float x) {
+    if constexpr (DT == I8F_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+    else return __half2float(__float2half_rn(x));
+}
+template <int DT>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (DT == I8F_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+template <int DT>
+__device__ __forceinline__ float unpack_lo(uint32_t w) {
+    if constexpr (DT == I8F_BF16) return __uint_as_float(w << 16);
+    else return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xFFFFu)));
+}
+template <int DT>
+__device__ __forceinline__ float unpack_hi(uint32_t w) {
+    if constexpr (DT == I8F_BF16) return __uint_as_float(w & 0xFFFF0000u);
+    else return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+}
+
+__device__ __forceinline__ float load_as_f32(const void* p, int dt, long long i) {
+    if (dt == I8F_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    if (dt == I8F_F16) return __half2float(static_cast<const __half*>(p)[i]);
+    return static_cast<const float*>(p)[i];
+}
+
+// Store 32 consecutive outputs of one row.  `y` already holds the values to
+// store (exactly representable in OUT when they were rounded by the caller).
+template <int OUT>
+__device__ __forceinline__ void store_row32(const GemmParams& p, long long row, int col, const float (&y)[32]) {
+    using T16 = unsigned short;
+    T16* dst = static_cast<T16*>(p.out) + row * p.ldo + col;
+    if (p.vec_ok && col + 32 <= p.N) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack2<OUT>(y[8 * g + 0], y[8 * g + 1]);
+            o.y = pack2<OUT>(y[8 * g + 2], y[8 * g + 3]);
+            o.z = pack2<OUT>(y[8 * g + 4], y[8 * g + 5]);
+            o.w = pack2<OUT>(y[8 * g + 6], y[8 * g + 7]);
+            d4[g] = o;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col + j < p.N) {
+                const uint32_t w = pack2<OUT>(y[j], 0.f);
+                dst[j] = static_cast<T16>(w & 0xFFFFu);
+            }
+        }
+    }
+}
+
+template <int OUT>
+__device__ __forceinline__ void load_row32(const GemmParams& p, long long row, int col, float (&y)[32]) {
+    using T16 = unsigned short;
+    const T16* src = static_cast<const T16*>(p.out) + row * p.ldo + col;
+    if (p.vec_ok && col + 32 <= p.N) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint4 o = s4[g];
+            const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[8 * g + 2 * i] = unpack_lo<OUT>(w[i]);
+                y[8 * g + 2 * i + 1] = unpack_hi<OUT>(w[i]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = (col + j < p.N) ? unpack_lo<OUT>(src[j]) : 0.f;
+    }
+}
+
+// One 32-column chunk of one accumulator row -> global memory.
+template <int OUT>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, int col, const uint32_t (&v)[32],
+                                               float row_scale, float ws_scalar) {
+    float y[32];
+    if (p.epi_mode == kEpiDequant) {
+        const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
+        const bool single = p.epi_order == I8F_EPI_SINGLE;
+        if (!per_ch) {
+            // reference order: (ws * xs) first, then times the accumulator
+            const float total = __fmul_rn(ws_scalar, row_scale);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), total);
+        } else if (!single) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float ws = (col + j < p.N) ? __ldg(p.w_scale + col + j) : 0.f;
+                y[j] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[j])), row_scale), ws);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float ws = (col + j < p.N) ? __ldg(p.w_scale + col + j) : 0.f;
+                y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), __fmul_rn(row_scale, ws));
+            }
+        }
+        if (p.bias != nullptr) {
+            if (!single) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float b = (col + j < p.N) ? load_as_f32(p.bias, p.bias_dtype, col + j) : 0.f;
+                    y[j] = __fadd_rn(round_out<OUT>(y[j]), round_out<OUT>(b));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float b = (col + j < p.N) ? load_as_f32(p.bias, p.bias_dtype, col + j) : 0.f;
+                    y[j] = __fadd_rn(y[j], b);
+                }
+            }
+        }
+    } else if (p.epi_mode == kEpiCast) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+    } else {  // kEpiAccum: out = round(out + round(acc))
+        load_row32<OUT>(p, row, col, y);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], round_out<OUT>(__uint_as_float(v[j])));
+    }
+    store_row32<OUT>(p, row, col, y);
+}
+
+__device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long row, int col, const uint32_t (&v)[32]) {
+    int* dst = static_cast<int*>(p.out) + row * p.ldo + col;
+    if (p.vec_ok && col + 32 <= p.N) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < p.N) dst[j] = static_cast<int>(v[j]);
+    }
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    using C = Cfg<BN>;
+    constexpr int kElemsPerStage = (KIND == kKindI8) ? kStageRowBytes : kStageRowBytes / 2;
+    constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, kBM, BN)
+                                : (KIND == kKindBF16) ? make_idesc(kDFmtF32, kFmtBF16, kBM, BN)
+                                                      : make_idesc(kDFmtF32, kFmtF16, kBM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+    const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+    // barrier block: full[kStages], empty[kStages], acc_full[2], acc_empty[2], tmem slot, abort flag
+    const uint32_t full0 = bar_base;
+    const uint32_t empty0 = bar_base + 8 * C::kStages;
+    const uint32_t accfull0 = bar_base + 16 * C::kStages;
+    const uint32_t accempty0 = accfull0 + 16;
+    const uint32_t tmem_slot = accempty0 + 16;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + 16 * C::kStages + 32);
+    volatile int* abort_flag =
+        reinterpret_cast<volatile int*>(gen_base + C::kStages * C::kStageBytes + 16 * C::kStages + 36);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accfull0 + 8 * b, 1);
+            mbar_init(accempty0 + 8 * b, 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc<C::kTmemCols>(tmem_slot);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.status, kStEmptyWait)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * C::kStageBytes;
+                    const uint32_t b_dst = a_dst + C::kABytes;
+                    mbar_arrive_expect_tx(full0 + 8 * stage, C::kStageBytes);
+                    tma_load_2d(a_dst, &tmA, full0 + 8 * stage, kb * kElemsPerStage, m_blk * kBM);
+                    tma_load_2d(b_dst, &tmB, full0 + 8 * stage, kb * kElemsPerStage, n_blk * BN);
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int buf = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                if (!mbar_wait_bounded(accempty0 + 8 * buf, acc_phase ^ 1u, abort_flag, p.status, kStAccEmptyWait)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + stage * C::kStageBytes;
+                    const uint64_t adesc = make_smem_desc_sw128(a_src);
+                    const uint64_t bdesc = make_smem_desc_sw128(a_src + C::kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // +32 bytes of K per instruction: 2 in the (address >> 4) field
+                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                        if constexpr (KIND == kKindI8) mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                        else mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                    }
+                    mma_commit(empty0 + 8 * stage);  // stage reusable once these MMAs have read it
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mma_commit(accfull0 + 8 * buf);  // accumulator complete
+                buf ^= 1;
+                if (buf == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        int buf = 0;
+        uint32_t acc_phase = 0;
+        const float ws_scalar =
+            (p.epi_mode == kEpiDequant && p.w_scale_mode == I8F_WSCALE_TENSOR) ? __ldg(p.w_scale) : 0.f;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            int m_blk, n_blk;
+            tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
+            if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
+            tc_fence_after_sync();
+            const long long row = static_cast<long long>(m_blk) * kBM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            const float row_scale = (p.epi_mode == kEpiDequant && row_ok) ? __ldg(p.a_scale + row) : 0.f;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_addr + c * 32, v);
+                tmem_ld_wait();
+                const int col = n_blk * BN + c * 32;
+                if (row_ok && col < p.N) {
+                    if (p.epi_mode == kEpiI32) store_i32_row32(p, row, col, v);
+                    else if (p.out_dtype == I8F_BF16) epilogue_chunk<I8F_BF16>(p, row, col, v, row_scale, ws_scalar);
+                    else epilogue_chunk<I8F_F16>(p, row, col, v, row_scale, ws_scalar);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty0 + 8 * buf);
+            buf ^= 1;
+            if (buf == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // common teardown (also reached after an aborted wait)
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before the CTA exits
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<C::kTmemCols>(tmem_base);
+    }
+}
+
+// ------------------------------------------------------------------ host
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static EncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeFn>(f);
+    }();
+    return fn;
+}
+
+// K-major [rows, k_elems] matrix, box = one 128-byte span of K x box_rows, 128-byte swizzle.
+int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, int64_t k_elems, int64_t ld_elems,
+                     int box_rows) {
+    EncodeFn enc = get_encode_fn();
+    I8F_REQUIRE(enc != nullptr, I8F_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const int esz = kind == kKindI8 ? 1 : 2;
+    const CUtensorMapDataType dt = kind == kKindI8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : kind == kKindBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * esz};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kStageRowBytes / esz), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    I8F_REQUIRE(r == CUDA_SUCCESS, I8F_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return I8F_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+template <int KIND, int BN>
+int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K, GemmParams p,
+                cudaStream_t st) {
+    using C = Cfg<BN>;
+    CUtensorMap tmA, tmB;
+    int rc = make_operand_map(&tmA, KIND, a, M, K, lda, kBM);
+    if (rc != I8F_OK) return rc;
+    rc = make_operand_map(&tmB, KIND, b, N, K, ldb, BN);
+    if (rc != I8F_OK) return rc;
+    const int esz = KIND == kKindI8 ? 1 : 2;
+    const int k_per_stage = kStageRowBytes / esz;
+    p.M = static_cast<int>(M);
+    p.N = static_cast<int>(N);
+    p.num_k_blocks = static_cast<int>((K + k_per_stage - 1) / k_per_stage);
+    p.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
+    p.tiles_n = static_cast<int>((N + BN - 1) / BN);
+    p.status = device_status_word();
+    I8F_REQUIRE(p.status != nullptr, I8F_ERR_CUDA, "device status word unavailable");
+    auto kern = gemm_tcgen05_kernel<KIND, BN>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
+        attr_done[dev] = true;
+    }
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, kThreads, C::kSmemBytes, st>>>(tmA, tmB, p);
+    return check_launch("gemm_tcgen05_kernel");
+}
+
+template <int KIND>
+int launch_gemm_bn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
+                   const GemmParams& p, cudaStream_t st) {
+    // wide tiles for wide outputs; narrow ones when N is small (LoRA rank)
+    if (N > 128) return launch_gemm<KIND, 256>(a, lda, b, ldb, M, N, K, p, st);
+    if (N > 64) return launch_gemm<KIND, 128>(a, lda, b, ldb, M, N, K, p, st);
+    return launch_gemm<KIND, 64>(a, lda, b, ldb, M, N, K, p, st);
+}
+
+int check_operands(const void* a, int64_t lda, const void* b, int64_t ldb, int esz, int64_t M, int64_t N, int64_t K) {
+    I8F_REQUIRE(M > 0 && N > 0 && K > 0, I8F_ERR_INVALID_ARG, "empty problem M=%lld N=%lld K=%lld", (long long)M,
+                (long long)N, (long long)K);
+    I8F_REQUIRE(M < (1LL << 31) - 256 && N < (1LL << 31) - 256 && K < (1LL << 31) - 256, I8F_ERR_UNSUPPORTED,
+                "dimension too large");
+    I8F_REQUIRE(a != nullptr && b != nullptr, I8F_ERR_INVALID_ARG, "NULL operand");
+    I8F_REQUIRE(lda >= K && ldb >= K, I8F_ERR_INVALID_ARG, "operand pitch smaller than K");
+    I8F_REQUIRE(aligned16(a) && aligned16(b), I8F_ERR_ALIGNMENT, "operands must be 16-byte aligned (TMA)");
+    I8F_REQUIRE((lda * esz) % 16 == 0 && (ldb * esz) % 16 == 0, I8F_ERR_ALIGNMENT,
+                "operand row pitch must be a multiple of 16 bytes (TMA): lda=%lld ldb=%lld elem=%d", (long long)lda,
+                (long long)ldb, esz);
+    return I8F_OK;
+}
+
+}  // namespace
+}  // namespace i8f
+
+using namespace i8f;
+
+extern "C" {
+
+int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldacc, int64_t M,
+                    int64_t N, int64_t K, void* stream) {
+    int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(acc != nullptr && ldacc >= N, I8F_ERR_INVALID_ARG, "bad accumulator output");
+    GemmParams p{};
+    p.out = acc;
+    p.ldo = ldacc;
+    p.epi_mode = kEpiI32;
+    p.vec_ok = aligned16(acc) && (ldacc % 4 == 0);
+    return launch_gemm_bn<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+}
+
+int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                    const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out, int out_dtype,
+                    int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
+    int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(a_scale != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL scale pointer");
+    I8F_REQUIRE(w_scale_mode == I8F_WSCALE_TENSOR || w_scale_mode == I8F_WSCALE_CHANNEL, I8F_ERR_INVALID_ARG,
+                "unknown w_scale_mode %d", w_scale_mode);
+    I8F_REQUIRE(out != nullptr && ldo >= N, I8F_ERR_INVALID_ARG, "bad output");
+    I8F_REQUIRE(out_dtype == I8F_BF16 || out_dtype == I8F_F16, I8F_ERR_UNSUPPORTED, "out_dtype must be bf16 or f16");
+    I8F_REQUIRE(bias == nullptr || dtype_size(bias_dtype) != 0, I8F_ERR_INVALID_ARG, "unknown bias dtype %d", bias_dtype);
+    I8F_REQUIRE(epilogue_order == I8F_EPI_PYTORCH || epilogue_order == I8F_EPI_SINGLE, I8F_ERR_INVALID_ARG,
+                "unknown epilogue_order %d", epilogue_order);
+    GemmParams p{};
+    p.out = out;
+    p.ldo = ldo;
+    p.out_dtype = out_dtype;
+    p.a_scale = a_scale;
+    p.w_scale = w_scale;
+    p.w_scale_mode = w_scale_mode;
+    p.bias = bias;
+    p.bias_dtype = bias_dtype;
+    p.epi_mode = kEpiDequant;
+    p.epi_order = epilogue_order;
+    p.vec_ok = aligned16(out) && (ldo % 8 == 0);
+    return launch_gemm_bn<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+}
+
+size_t i8f_linear_workspace_bytes(int64_t M, int64_t K) {
+    if (M <= 0 || K <= 0) return 0;
+    const size_t q = (static_cast<size_t>(M) * static_cast<size_t>(K) + 255) & ~static_cast<size_t>(255);
+    const size_t s = (static_cast<size_t>(M) * sizeof(float) + 255) & ~static_cast<size_t>(255);
+    return q + s;
+}
+
+int i8f_linear_forward(const void* x, int x_dtype, int64_t ldx, int hadamard128, const int8_t* w, int64_t ldw,
+                       const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out,
+                       int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+    I8F_REQUIRE(M > 0 && N > 0 && K > 0, I8F_ERR_INVALID_ARG, "empty problem");
+    I8F_REQUIRE(K % 16 == 0, I8F_ERR_ALIGNMENT, "K=%lld must be a multiple of 16", (long long)K);
+    const size_t need = i8f_linear_workspace_bytes(M, K);
+    I8F_REQUIRE(workspace != nullptr && workspace_bytes >= need, I8F_ERR_WORKSPACE,
+                "workspace too small: have %zu bytes, need %zu", workspace_bytes, need);
+    I8F_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, I8F_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    int8_t* q = static_cast<int8_t*>(workspace);
+    float* xs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ((static_cast<size_t>(M) * K + 255) & ~size_t(255)));
+    int rc = i8f_quant_rowwise(x, x_dtype, M, K, ldx, q, K, xs, hadamard128, nullptr, stream);
+    if (rc != I8F_OK) return rc;
+    return i8f_linear_w8a8(q, K, xs, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
+                           epilogue_order, stream);
+}
+
+int i8f_lora_down(const void* x, int64_t ldx, const void* lora_a, int64_t lda, void* t, int64_t ldt, int dtype, int64_t M,
+                  int64_t K, int64_t r, void* stream) {
+    I8F_REQUIRE(dtype == I8F_BF16 || dtype == I8F_F16, I8F_ERR_UNSUPPORTED, "dtype must be bf16 or f16");
+    int rc = check_operands(x, ldx, lora_a, lda, 2, M, r, K);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(t != nullptr && ldt >= r, I8F_ERR_INVALID_ARG, "bad output");
+    GemmParams p{};
+    p.out = t;
+    p.ldo = ldt;
+    p.out_dtype = dtype;
+    p.epi_mode = kEpiCast;
+    p.vec_ok = aligned16(t) && (ldt % 8 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == I8F_BF16) return launch_gemm_bn<kKindBF16>(x, ldx, lora_a, lda, M, r, K, p, st);
+    return launch_gemm_bn<kKindF16>(x, ldx, lora_a, lda, M, r, K, p, st);
+}
+
+int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb, void* y, int64_t ldy, int dtype,
+                    int64_t M, int64_t N, int64_t r, void* stream) {
+    I8F_REQUIRE(dtype == I8F_BF16 || dtype == I8F_F16, I8F_ERR_UNSUPPORTED, "dtype must be bf16 or f16");
+    int rc = check_operands(t, ldt, lora_b, ldb, 2, M, N, r);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(y != nullptr && ldy >= N, I8F_ERR_INVALID_ARG, "bad output");
+    GemmParams p{};
+    p.out = y;
+    p.ldo = ldy;
+    p.out_dtype = dtype;
+    p.epi_mode = kEpiAccum;
+    p.vec_ok = aligned16(y) && (ldy % 8 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == I8F_BF16) return launch_gemm_bn<kKindBF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
+    return launch_gemm_bn<kKindF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,274 @@
+// Stochastic-rounding merge of a low-rank update into int8 weights.
+//
+// A CTA owns one 128-column block of K (so the optional Hadamard rotation of
+// the delta is CTA-local) and walks down a band of rows, 32 rows at a time.
+// The [r x 128] slice of `down` is staged once in shared memory as fp32; each
+// thread accumulates a 2 x 8 patch of the delta in registers with the rank
+// index ascending (acc = acc + up*down, separate multiply and add, which fixes
+// the fp32 rounding), then scales, rotates, divides by the weight scale,
+// rounds stochastically and adds into the int8 weights.  The only HBM
+// traffic is the weights (read + write), the factors and, if supplied, the
+// uniforms.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+
+namespace i8f {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRowsPerIter = 32;
+constexpr float kNormF32 = 0.088388346135616302f;
+
+__device__ __forceinline__ float load_f(const void* p, int dt, long long i) {
+    if (dt == I8F_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    if (dt == I8F_F16) return __half2float(static_cast<const __half*>(p)[i]);
+    return static_cast<const float*>(p)[i];
+}
+
+// Philox4x32-10, counter (c0, c1, 0, 0), key (k0, k1).
+__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
+    uint32_t x0 = c0, x1 = c1, x2 = 0u, x3 = 0u;
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, x0), lo0 = 0xD2511F53u * x0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, x2), lo1 = 0xCD9E8D57u * x2;
+        const uint32_t n0 = hi1 ^ x1 ^ k0, n2 = hi0 ^ x3 ^ k1;
+        x0 = n0; x1 = lo1; x2 = n2; x3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return make_uint4(x0, x1, x2, x3);
+}
+__device__ __forceinline__ float u01(uint32_t w) { return static_cast<float>(w >> 8) * 5.9604644775390625e-8f; }
+
+// floor(x/ws) + [u < frac], clamped to int8 range.
+__device__ __forceinline__ int sr_round(float delta, float ws, float u) {
+    const float xs = __fdiv_rn(delta, ws);
+    const float fl = floorf(xs);
+    const float fr = __fsub_rn(xs, fl);
+    const float r = (u < fr) ? __fadd_rn(fl, 1.0f) : fl;
+    return static_cast<int>(fminf(fmaxf(r, -128.0f), 127.0f));
+}
+
+__device__ __forceinline__ void wht128_lanes16(float (&v)[8], int lane) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = __fadd_rn(a, b);
+                v[i + h] = __fsub_rn(a, b);
+            }
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1) {
+        const bool upper = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float p = __shfl_xor_sync(0xFFFFFFFFu, v[i], d);
+            v[i] = upper ? __fsub_rn(p, v[i]) : __fadd_rn(v[i], p);
+        }
+    }
+}
+
+// 16-byte chunk swizzle of a 128-float row so that the 16 threads of a row
+// group, each reading 8 consecutive floats as two float4, hit distinct banks.
+__device__ __forceinline__ int swz(int col) {
+    const int chunk = col >> 2;
+    return ((chunk ^ ((chunk >> 3) & 1)) << 2) | (col & 3);
+}
+
+template <bool HAD>
+__global__ void __launch_bounds__(kThreads)
+lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict__ w_scale, int ws_mode,
+                  const void* __restrict__ up, long long ldup, const void* __restrict__ down, long long lddown, int fdt,
+                  int N, int K, int r, float lora_scale, const float* __restrict__ uniforms, unsigned long long seed,
+                  int rows_per_cta, int w_vec_ok) {
+    extern __shared__ float smem[];
+    float* s_down = smem;            // [r][128] swizzled
+    float* s_up = smem + r * 128;    // [32][r + 1] (padded: the two row pairs of a warp land in different banks)
+    const int rs = r + 1;
+    const int k0 = blockIdx.x * 128;
+    for (int idx = threadIdx.x; idx < r * 128; idx += kThreads) {
+        const int j = idx >> 7, c = idx & 127;
+        s_down[j * 128 + swz(c)] = (k0 + c < K) ? load_f(down, fdt, static_cast<long long>(j) * lddown + k0 + c) : 0.f;
+    }
+    const int row_begin = blockIdx.y * rows_per_cta;
+    const int row_end = min(N, row_begin + rows_per_cta);
+    const int tr = threadIdx.x >> 4;   // row pair index 0..15
+    const int tc = threadIdx.x & 15;   // column octet
+    const int lane = threadIdx.x & 31;
+    const int kc = k0 + tc * 8;
+    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
+
+    for (int n0 = row_begin; n0 < row_end; n0 += kRowsPerIter) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kRowsPerIter * r; idx += kThreads) {
+            const int rr = idx / r, j = idx - rr * r;
+            s_up[rr * rs + j] = (n0 + rr < row_end) ? load_f(up, fdt, static_cast<long long>(n0 + rr) * ldup + j) : 0.f;
+        }
+        __syncthreads();
+        float acc[2][8];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
+        const float* u0p = s_up + (2 * tr) * rs;
+        const float* u1p = u0p + rs;
+        const int c0 = swz(tc * 8), c1 = swz(tc * 8 + 4);
+        for (int j = 0; j < r; ++j) {
+            const float4 da = *reinterpret_cast<const float4*>(s_down + j * 128 + c0);
+            const float4 db = *reinterpret_cast<const float4*>(s_down + j * 128 + c1);
+            const float d[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+            const float ua = u0p[j], ub = u1p[j];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                acc[0][c] = __fadd_rn(acc[0][c], __fmul_rn(ua, d[c]));
+                acc[1][c] = __fadd_rn(acc[1][c], __fmul_rn(ub, d[c]));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], lora_scale);
+            if constexpr (HAD) {
+                wht128_lanes16(acc[i], lane);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], kNormF32);
+            }
+            const int n = n0 + 2 * tr + i;
+            if (n >= row_end || kc >= K) continue;
+            const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
+            float u[8];
+            if (uniforms != nullptr) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) u[c] = (kc + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + kc + c) : 1.f;
+            } else {
+                const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), key0, key1);
+                const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, key0, key1);
+                u[0] = u01(ra.x); u[1] = u01(ra.y); u[2] = u01(ra.z); u[3] = u01(ra.w);
+                u[4] = u01(rb.x); u[5] = u01(rb.y); u[6] = u01(rb.z); u[7] = u01(rb.w);
+            }
+            int8_t* wp = w + static_cast<long long>(n) * ldw + kc;
+            if (w_vec_ok && kc + 8 <= K) {
+                uint2 old = *reinterpret_cast<const uint2*>(wp);
+                uint32_t ow[2] = {old.x, old.y};
+                uint32_t nw[2] = {0u, 0u};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int wo = static_cast<int>(static_cast<int8_t>((ow[c >> 2] >> (8 * (c & 3))) & 0xFFu));
+                    const int s = max(-128, min(127, wo + sr_round(acc[i][c], ws, u[c])));
+                    nw[c >> 2] |= (static_cast<uint32_t>(s) & 0xFFu) << (8 * (c & 3));
+                }
+                *reinterpret_cast<uint2*>(wp) = make_uint2(nw[0], nw[1]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (kc + c < K) {
+                        const int s = max(-128, min(127, static_cast<int>(wp[c]) + sr_round(acc[i][c], ws, u[c])));
+                        wp[c] = static_cast<int8_t>(s);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Element-wise stochastic rounding of an fp32 delta; one thread per group of
+// four columns (one Philox block).
+__global__ void __launch_bounds__(kThreads)
+stochastic_round_kernel(const float* __restrict__ delta, long long ldd, const float* __restrict__ w_scale, int ws_mode,
+                        int8_t* __restrict__ d8, long long ldq, int N, int K, const float* __restrict__ uniforms,
+                        unsigned long long seed) {
+    const int groups = (K + 3) >> 2;
+    const long long total = static_cast<long long>(N) * groups;
+    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
+    for (long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; g < total;
+         g += static_cast<long long>(gridDim.x) * kThreads) {
+        const int n = static_cast<int>(g / groups);
+        const int kg = static_cast<int>(g - static_cast<long long>(n) * groups);
+        const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
+        float u[4];
+        if (uniforms != nullptr) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) u[c] = (4 * kg + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + 4 * kg + c) : 1.f;
+        } else {
+            const uint4 rr = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kg), key0, key1);
+            u[0] = u01(rr.x); u[1] = u01(rr.y); u[2] = u01(rr.z); u[3] = u01(rr.w);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int k = 4 * kg + c;
+            if (k < K) d8[static_cast<long long>(n) * ldq + k] = static_cast<int8_t>(sr_round(__ldg(delta + static_cast<long long>(n) * ldd + k), ws, u[c]));
+        }
+    }
+}
+
+}  // namespace
+}  // namespace i8f
+
+using namespace i8f;
+
+extern "C" {
+
+int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode, const void* up, int64_t ldup,
+                      const void* down, int64_t lddown, int factor_dtype, int64_t N, int64_t K, int64_t r,
+                      float lora_scale, int hadamard128, const float* uniforms, uint64_t seed, void* stream) {
+    I8F_REQUIRE(N >= 0 && K >= 0 && r >= 0, I8F_ERR_INVALID_ARG, "negative shape");
+    if (N == 0 || K == 0) return I8F_OK;
+    I8F_REQUIRE(w != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL weight or scale");
+    I8F_REQUIRE(r == 0 || (up != nullptr && down != nullptr), I8F_ERR_INVALID_ARG, "NULL factor");
+    I8F_REQUIRE(dtype_size(factor_dtype) != 0, I8F_ERR_INVALID_ARG, "unknown factor dtype %d", factor_dtype);
+    I8F_REQUIRE(w_scale_mode == I8F_WSCALE_TENSOR || w_scale_mode == I8F_WSCALE_CHANNEL, I8F_ERR_INVALID_ARG,
+                "unknown w_scale_mode %d", w_scale_mode);
+    I8F_REQUIRE(ldw >= K && ldup >= r && lddown >= K, I8F_ERR_INVALID_ARG, "pitch smaller than the row length");
+    I8F_REQUIRE(!hadamard128 || K % 128 == 0, I8F_ERR_UNSUPPORTED, "Hadamard rotation needs K %% 128 == 0");
+    I8F_REQUIRE(N < (1LL << 31) && K < (1LL << 31), I8F_ERR_UNSUPPORTED, "dimension too large");
+    const size_t smem = (static_cast<size_t>(r) * 128 + static_cast<size_t>(kRowsPerIter) * (r + 1)) * sizeof(float);
+    I8F_REQUIRE(smem <= 200 * 1024, I8F_ERR_UNSUPPORTED, "rank %lld too large for one pass (max 320)", (long long)r);
+    const int col_blocks = static_cast<int>((K + 127) / 128);
+    // enough row bands to fill the GPU a few times over, each band a multiple of 32 rows
+    int bands = (148 * 4 + col_blocks - 1) / col_blocks;
+    const int max_bands = static_cast<int>((N + kRowsPerIter - 1) / kRowsPerIter);
+    if (bands > max_bands) bands = max_bands;
+    if (bands < 1) bands = 1;
+    if (bands > 65535) bands = 65535;
+    int rows_per_cta = static_cast<int>((N + bands - 1) / bands);
+    rows_per_cta = (rows_per_cta + kRowsPerIter - 1) / kRowsPerIter * kRowsPerIter;
+    bands = static_cast<int>((N + rows_per_cta - 1) / rows_per_cta);
+    const int w_vec_ok = ((reinterpret_cast<uintptr_t>(w) & 7u) == 0 && ldw % 8 == 0) ? 1 : 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid(col_blocks, bands);
+    auto launch = [&](auto kern) -> int {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        }
+        kern<<<grid, kThreads, smem, st>>>(w, ldw, w_scale, w_scale_mode, up, ldup, down, lddown, factor_dtype,
+                                           static_cast<int>(N), static_cast<int>(K), static_cast<int>(r), lora_scale,
+                                           uniforms, seed, rows_per_cta, w_vec_ok);
+        return check_launch("lora_merge_kernel");
+    };
+    return hadamard128 ? launch(lora_merge_kernel<true>) : launch(lora_merge_kernel<false>);
+}
+
+int i8f_stochastic_round(const float* delta, int64_t ldd, const float* w_scale, int w_scale_mode, int8_t* d8,
+                         int64_t ldq, int64_t N, int64_t K, const float* uniforms, uint64_t seed, void* stream) {
+    I8F_REQUIRE(N >= 0 && K >= 0, I8F_ERR_INVALID_ARG, "negative shape");
+    if (N == 0 || K == 0) return I8F_OK;
+    I8F_REQUIRE(delta != nullptr && d8 != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL pointer");
+    I8F_REQUIRE(ldd >= K && ldq >= K, I8F_ERR_INVALID_ARG, "pitch smaller than K");
+    I8F_REQUIRE(w_scale_mode == I8F_WSCALE_TENSOR || w_scale_mode == I8F_WSCALE_CHANNEL, I8F_ERR_INVALID_ARG,
+                "unknown w_scale_mode %d", w_scale_mode);
+    I8F_REQUIRE(N < (1LL << 31) && K < (1LL << 31), I8F_ERR_UNSUPPORTED, "dimension too large");
+    const long long total = N * ((K + 3) / 4);
+    long long blocks = (total + kThreads - 1) / kThreads;
+    if (blocks > 148LL * 16) blocks = 148LL * 16;
+    stochastic_round_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        delta, ldd, w_scale, w_scale_mode, d8, ldq, static_cast<int>(N), static_cast<int>(K), uniforms, seed);
+    return check_launch("stochastic_round_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,344 @@
+// Absmax int8 quantisation of matrix rows, optionally fused with the
+// 128-block Walsh-Hadamard rotation.  HBM-bound: every element is read once
+// with 128-bit loads, kept in registers across the absmax reduction, and
+// written once as int8.
+//
+// Thread layout: a row is owned by TPR threads (power of two, 16..256); thread
+// t holds the 8-element vectors t, t+TPR, t+2*TPR, ...  A 128-element
+// Hadamard block is therefore spread over 16 consecutive lanes of one warp:
+// butterfly strides 1,2,4 stay inside a thread, strides 8..64 are lane
+// exchanges (shuffle-xor 1,2,4,8).  The stage order and the a+b / a-b
+// assignment follow the natural-order in-place butterfly, which fixes the
+// fp32 rounding of every partial sum.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+
+namespace i8f {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr float kNormHalf = 0.08837890625f;      // bf16(1/sqrt(128)) == fp16(1/sqrt(128))
+constexpr float kNormF32 = 0.088388346135616302f;  // fp32(1)/fp32(sqrt(128))
+constexpr float kScaleFloor = 1e-30f;
+
+enum Mode : int { kRowwise = 0, kAbsmaxOnly = 1, kGlobalScale = 2 };
+
+template <int DT>
+__device__ __forceinline__ void load8(const void* base, int64_t elem_off, float (&v)[8]) {
+    if constexpr (DT == I8F_BF16) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + elem_off));
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    } else if constexpr (DT == I8F_F16) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(base) + elem_off));
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            const float2 f = __half22float2(h);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
+        const float4 a = __ldg(p), b = __ldg(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
+// Round an fp32 value to the storage type and return it as fp32.
+template <int DT>
+__device__ __forceinline__ float round_to_dt(float x) {
+    if constexpr (DT == I8F_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+    else if constexpr (DT == I8F_F16) return __half2float(__float2half_rn(x));
+    else return x;
+}
+
+template <int DT>
+__device__ __forceinline__ void store8(void* base, int64_t elem_off, const float (&v)[8]) {
+    if constexpr (DT == I8F_BF16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(base) + elem_off) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if constexpr (DT == I8F_F16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(static_cast<__half*>(base) + elem_off) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(base) + elem_off);
+        p[0] = make_float4(v[0], v[1], v[2], v[3]);
+        p[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+// 128-point Walsh-Hadamard butterfly over 16 lanes x 8 registers.
+__device__ __forceinline__ void wht128(float (&v)[8], int lane) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = __fadd_rn(a, b);
+                v[i + h] = __fsub_rn(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1) {
+        const bool upper = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float p = __shfl_xor_sync(0xFFFFFFFFu, v[i], d);
+            v[i] = upper ? __fsub_rn(p, v[i]) : __fadd_rn(v[i], p);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv) {
+    int qa = __float2int_rn(__fmul_rn(a, inv));
+    int qb = __float2int_rn(__fmul_rn(b, inv));
+    int qc = __float2int_rn(__fmul_rn(c, inv));
+    int qd = __float2int_rn(__fmul_rn(d, inv));
+    qa = max(-128, min(127, qa));
+    qb = max(-128, min(127, qb));
+    qc = max(-128, min(127, qc));
+    qd = max(-128, min(127, qd));
+    return (static_cast<uint32_t>(qa) & 0xFFu) | ((static_cast<uint32_t>(qb) & 0xFFu) << 8) |
+           ((static_cast<uint32_t>(qc) & 0xFFu) << 16) | ((static_cast<uint32_t>(qd) & 0xFFu) << 24);
+}
+
+// DT: storage type of x.  VPT: 8-element vectors per thread.  HAD: rotate.
+// ROT_F32: rotate in fp32 with the fp32 norm and no rounding (weight rule);
+// otherwise the rotated value is rounded to DT (activation rule).
+template <int DT, int VPT, bool HAD, bool ROT_F32, int MODE>
+__global__ void __launch_bounds__(kThreads)
+quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, int8_t* __restrict__ q, int64_t ldq,
+                  float* __restrict__ scale, void* __restrict__ xrot, float* __restrict__ gmax, int tpr_log2) {
+    __shared__ float s_part[kThreads / 32];
+    const int tpr = 1 << tpr_log2;
+    const int rows_per_cta = kThreads >> tpr_log2;
+    const int t = threadIdx.x & (tpr - 1);
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + (threadIdx.x >> tpr_log2);
+    const bool row_ok = row < M;
+    const int nvec = static_cast<int>(K >> 3);
+
+    float v[VPT][8];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int vec = i * tpr + t;
+        if (row_ok && vec < nvec) {
+            load8<DT>(x, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+        }
+    }
+
+    if constexpr (HAD) {
+        constexpr float norm = (ROT_F32 || DT == I8F_F32) ? kNormF32 : kNormHalf;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            wht128(v[i], lane);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float r = __fmul_rn(v[i][j], norm);
+                v[i][j] = ROT_F32 ? r : round_to_dt<DT>(r);
+            }
+            if constexpr (MODE == kRowwise) {
+                const int vec = i * tpr + t;
+                if (xrot != nullptr && row_ok && vec < nvec) store8<DT>(xrot, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
+            }
+        }
+    }
+
+    float amax = 0.f;
+    if constexpr (MODE != kGlobalScale) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+        // reduce over the lanes of this row that share a warp
+        const int span = tpr < 32 ? tpr : 32;
+        for (int d = 1; d < span; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+        if (tpr > 32 || MODE == kAbsmaxOnly) {
+            if (lane == 0) s_part[threadIdx.x >> 5] = amax;
+            __syncthreads();
+            if constexpr (MODE == kAbsmaxOnly) {
+                if (threadIdx.x == 0) {
+                    float m = 0.f;
+                    for (int w = 0; w < kThreads / 32; ++w) m = fmaxf(m, s_part[w]);
+                    // non-negative floats order like their bit patterns
+                    atomicMax(reinterpret_cast<int*>(gmax), __float_as_int(m));
+                }
+                return;
+            } else {
+                const int warps_per_row = tpr >> 5;
+                const int first = (threadIdx.x >> tpr_log2) * warps_per_row;
+                float m = 0.f;
+                for (int w = 0; w < warps_per_row; ++w) m = fmaxf(m, s_part[first + w]);
+                amax = m;
+            }
+        }
+    } else {
+        amax = *gmax;
+    }
+
+    const float sc = fmaxf(__fdiv_rn(amax, 127.0f), kScaleFloor);
+    const float inv = __fdiv_rn(1.0f, sc);
+    if constexpr (MODE == kRowwise) {
+        if (row_ok && t == 0) scale[row] = sc;
+    } else {
+        if (blockIdx.x == 0 && threadIdx.x == 0) scale[0] = sc;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int vec = i * tpr + t;
+        if (row_ok && vec < nvec) {
+            uint2 o;
+            o.x = quant4(v[i][0], v[i][1], v[i][2], v[i][3], inv);
+            o.y = quant4(v[i][4], v[i][5], v[i][6], v[i][7], inv);
+            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = o;
+        }
+    }
+}
+
+struct Plan {
+    int tpr_log2;
+    int vpt;
+};
+
+// Pick threads-per-row and vectors-per-thread: prefer 4 vectors (64 bytes of
+// bf16) in flight per thread, grow the row group up to the whole CTA, then
+// grow the per-thread count up to 16.
+inline bool make_plan(int64_t K, Plan* p) {
+    const int64_t nvec = K / 8;
+    int tpr_log2 = 4;
+    while (tpr_log2 < 8 && (nvec + (int64_t(1) << tpr_log2) - 1) / (int64_t(1) << tpr_log2) > 4) ++tpr_log2;
+    const int64_t need = (nvec + (int64_t(1) << tpr_log2) - 1) >> tpr_log2;
+    int vpt = 1;
+    while (vpt < need) vpt <<= 1;
+    if (vpt > 16) return false;
+    p->tpr_log2 = tpr_log2;
+    p->vpt = vpt;
+    return true;
+}
+
+template <int DT, bool HAD, bool ROT_F32, int MODE>
+int launch_vpt(const Plan& p, const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t ldq, float* scale,
+               void* xrot, float* gmax, cudaStream_t st) {
+    const int rows_per_cta = kThreads >> p.tpr_log2;
+    const unsigned grid = static_cast<unsigned>((M + rows_per_cta - 1) / rows_per_cta);
+#define I8F_LAUNCH(V)                                                                                              \
+    quant_rows_kernel<DT, V, HAD, ROT_F32, MODE><<<grid, kThreads, 0, st>>>(x, M, K, ldx, q, ldq, scale, xrot, gmax, \
+                                                                            p.tpr_log2)
+    switch (p.vpt) {
+        case 1: I8F_LAUNCH(1); break;
+        case 2: I8F_LAUNCH(2); break;
+        case 4: I8F_LAUNCH(4); break;
+        case 8: I8F_LAUNCH(8); break;
+        default: I8F_LAUNCH(16); break;
+    }
+#undef I8F_LAUNCH
+    return check_launch("quant_rows_kernel");
+}
+
+template <bool ROT_F32, int MODE>
+int launch_any(int dt, bool had, const Plan& p, const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t ldq,
+               float* scale, void* xrot, float* gmax, cudaStream_t st) {
+#define I8F_GO(DT)                                                                                           \
+    (had ? launch_vpt<DT, true, ROT_F32, MODE>(p, x, M, K, ldx, q, ldq, scale, xrot, gmax, st)                \
+         : launch_vpt<DT, false, ROT_F32, MODE>(p, x, M, K, ldx, q, ldq, scale, xrot, gmax, st))
+    switch (dt) {
+        case I8F_BF16: return I8F_GO(I8F_BF16);
+        case I8F_F16: return I8F_GO(I8F_F16);
+        default: return I8F_GO(I8F_F32);
+    }
+#undef I8F_GO
+}
+
+int check_common(const void* x, int dt, int64_t M, int64_t K, int64_t ldx, const int8_t* q, int64_t ldq, int had,
+                 Plan* plan) {
+    I8F_REQUIRE(dtype_size(dt) != 0, I8F_ERR_INVALID_ARG, "unknown dtype code %d", dt);
+    I8F_REQUIRE(M >= 0 && K >= 0, I8F_ERR_INVALID_ARG, "negative shape M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0 || K == 0) return I8F_OK;
+    I8F_REQUIRE(x != nullptr && q != nullptr, I8F_ERR_INVALID_ARG, "NULL input or output pointer");
+    I8F_REQUIRE(ldx >= K && ldq >= K, I8F_ERR_INVALID_ARG, "row pitch smaller than K");
+    I8F_REQUIRE(K % 8 == 0, I8F_ERR_UNSUPPORTED, "K=%lld must be a multiple of 8", (long long)K);
+    I8F_REQUIRE(!had || K % 128 == 0, I8F_ERR_UNSUPPORTED, "Hadamard rotation needs K %% 128 == 0 (K=%lld)", (long long)K);
+    I8F_REQUIRE(aligned16(x) && (ldx * dtype_size(dt)) % 16 == 0, I8F_ERR_ALIGNMENT,
+                "input must be 16-byte aligned with a 16-byte multiple row pitch");
+    I8F_REQUIRE((reinterpret_cast<uintptr_t>(q) & 7u) == 0 && ldq % 8 == 0, I8F_ERR_ALIGNMENT,
+                "int8 output must be 8-byte aligned with an 8-byte multiple row pitch");
+    I8F_REQUIRE(make_plan(K, plan), I8F_ERR_UNSUPPORTED, "K=%lld exceeds the 32768-element row limit", (long long)K);
+    return I8F_OK;
+}
+
+}  // namespace
+}  // namespace i8f
+
+using namespace i8f;
+
+extern "C" {
+
+int i8f_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t ldq,
+                      float* scale, int hadamard128, void* x_rot_out, void* stream) {
+    Plan plan{};
+    int rc = check_common(x, x_dtype, M, K, ldx, q, ldq, hadamard128, &plan);
+    if (rc != I8F_OK) return rc;
+    if (M == 0) return I8F_OK;
+    I8F_REQUIRE(scale != nullptr, I8F_ERR_INVALID_ARG, "scale is NULL");
+    if (K == 0) {
+        // empty rows: absmax 0 -> floor scale (matches the clamp on an empty reduction of zeros)
+        return fail(I8F_ERR_UNSUPPORTED, "K == 0 is not supported");
+    }
+    I8F_REQUIRE(x_rot_out == nullptr || aligned16(x_rot_out), I8F_ERR_ALIGNMENT, "x_rot_out must be 16-byte aligned");
+    return launch_any<false, kRowwise>(x_dtype, hadamard128 != 0, plan, x, M, K, ldx, q, ldq, scale,
+                                       hadamard128 ? x_rot_out : nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int i8f_quant_weight_rows(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw, int8_t* q, int64_t ldq,
+                          float* scale, int hadamard128, void* stream) {
+    Plan plan{};
+    int rc = check_common(w, w_dtype, N, K, ldw, q, ldq, hadamard128, &plan);
+    if (rc != I8F_OK) return rc;
+    if (N == 0) return I8F_OK;
+    I8F_REQUIRE(scale != nullptr && K > 0, I8F_ERR_INVALID_ARG, "scale is NULL or K == 0");
+    return launch_any<true, kRowwise>(w_dtype, hadamard128 != 0, plan, w, N, K, ldw, q, ldq, scale, nullptr, nullptr,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int i8f_quant_tensorwise(const void* x, int x_dtype, int64_t N, int64_t K, int64_t ldx, int8_t* q, int64_t ldq,
+                         float* scale_out, int hadamard128, void* scratch, void* stream) {
+    Plan plan{};
+    int rc = check_common(x, x_dtype, N, K, ldx, q, ldq, hadamard128, &plan);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(N > 0 && K > 0, I8F_ERR_INVALID_ARG, "empty tensor");
+    I8F_REQUIRE(scale_out != nullptr && scratch != nullptr, I8F_ERR_INVALID_ARG, "scale_out or scratch is NULL");
+    I8F_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 3u) == 0, I8F_ERR_ALIGNMENT, "scratch must be 4-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* gmax = static_cast<float*>(scratch);
+    cudaError_t e = cudaMemsetAsync(gmax, 0, sizeof(float), st);
+    if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    rc = launch_any<true, kAbsmaxOnly>(x_dtype, hadamard128 != 0, plan, x, N, K, ldx, q, ldq, scale_out, nullptr, gmax, st);
+    if (rc != I8F_OK) return rc;
+    return launch_any<true, kGlobalScale>(x_dtype, hadamard128 != 0, plan, x, N, K, ldx, q, ldq, scale_out, nullptr, gmax, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,175 @@
+/*
+ * libi8f -- C ABI of the B200 (sm_100a) W8A8 linear hot path.
+ *
+ * Each entry point replaces one piece of the Python/Triton hot path of the
+ * ComfyUI-INT8-Fast node pack; the file:line next to it names what it stands
+ * in for (paths are relative to that project).
+ *
+ * Conventions
+ *   - Every function returns I8F_OK (0) or a negative I8F_ERR_* code and never
+ *     throws; i8f_last_error() returns a thread-local description of the
+ *     last failure.
+ *   - All data pointers are device pointers on the current CUDA device and are
+ *     only borrowed until the enqueued work finishes.  Nothing is allocated,
+ *     nothing synchronises: work is enqueued on `stream` (a cudaStream_t
+ *     passed as void*; NULL means the legacy default stream).
+ *   - Matrices are row-major; `ld*` are row pitches in ELEMENTS.
+ *   - dtype codes: I8F_BF16, I8F_F16, I8F_F32.
+ *   - Kernels that feed the tensor cores through TMA need 16-byte aligned
+ *     base pointers and row pitches that are multiples of 16 bytes; this is
+ *     checked and reported as I8F_ERR_ALIGNMENT, never left undefined.
+ *   - Device-side waits are bounded; a wait that runs out is recorded in a
+ *     device status word readable with i8f_device_status().
+ */
+#ifndef I8F_H_
+#define I8F_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define I8F_VERSION 100
+
+#define I8F_OK 0
+#define I8F_ERR_INVALID_ARG (-1)
+#define I8F_ERR_ALIGNMENT (-2)
+#define I8F_ERR_UNSUPPORTED (-3)
+#define I8F_ERR_CUDA (-4)
+#define I8F_ERR_DEVICE (-5)
+#define I8F_ERR_WORKSPACE (-6)
+
+#define I8F_BF16 0
+#define I8F_F16 1
+#define I8F_F32 2
+
+/* weight-scale granularity */
+#define I8F_WSCALE_TENSOR 0  /* one fp32 value in device memory */
+#define I8F_WSCALE_CHANNEL 1 /* fp32[N] in device memory */
+
+/* epilogue rounding order */
+#define I8F_EPI_PYTORCH 0 /* round after scaling, round again after the bias add */
+#define I8F_EPI_SINGLE 1  /* one rounding after scale and bias */
+
+/* Library version (I8F_VERSION of the build). */
+int i8f_version(void);
+
+/* Thread-local text of the last error returned on this thread ("" if none). */
+const char* i8f_last_error(void);
+
+/* I8F_OK if the current device is compute capability 10.0, else I8F_ERR_DEVICE.
+ * Replaces the `x.is_cuda` / Triton-availability dispatch at int8_quant.py:72, :103
+ * with a hard requirement. */
+int i8f_device_check(void);
+
+/* Reads (and if `reset` is non-zero clears) the device status word of the
+ * current device.  0 means no bounded wait has run out since the last reset.
+ * Synchronises the device; meant for tests and diagnostics. */
+int i8f_device_status(int* status_out, int reset);
+
+/* Per-token absmax quantisation, optionally fused with the 128-block
+ * Walsh-Hadamard rotation.
+ *   x [M,K] (x_dtype) -> q int8 [M,K], scale fp32 [M]
+ *   scale = max(absmax/127, 1e-30); q = clamp(rint(x * (1/scale)), -128, 127)
+ * hadamard128 != 0 first rotates every 128-block of a row (K % 128 == 0
+ * required) and rounds the result to x_dtype; x_rot_out (may be NULL) receives
+ * that rotated tensor in x_dtype with pitch ldx.
+ * Replaces triton_quantize_rowwise (int8_fused_kernel.py:10-73),
+ * quantize_int8_axiswise (int8_quant.py:28-31) and rotate_activation
+ * (quarot.py:73-102) as called from int8_quant.py:741-744. */
+int i8f_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                      int8_t* q, int64_t ldq, float* scale, int hadamard128,
+                      void* x_rot_out, void* stream);
+
+/* Quantisation with one scale for the whole tensor (weights).
+ *   scale_out[0] = max(absmax(x)/127, 1e-30); q as above.
+ * `scratch` is 4 bytes of device memory owned by the caller (absmax exchange).
+ * hadamard128 rotates each row block in fp32 first (x_dtype must be I8F_F32).
+ * Replaces quantize_int8_tensorwise (int8_quant.py:23-26) and rotate_weight
+ * (quarot.py:42-70). */
+int i8f_quant_tensorwise(const void* x, int x_dtype, int64_t N, int64_t K, int64_t ldx,
+                         int8_t* q, int64_t ldq, float* scale_out, int hadamard128,
+                         void* scratch, void* stream);
+
+/* Per-output-channel weight quantisation (on-the-fly load path).
+ *   w [N,K] (w_dtype) -> q int8 [N,K], scale fp32 [N]; values are converted to
+ * fp32 first, hadamard128 rotates in fp32 (no intermediate rounding).
+ * Replaces int8_quant.py:597-613. */
+int i8f_quant_weight_rows(const void* w, int w_dtype, int64_t N, int64_t K, int64_t ldw,
+                          int8_t* q, int64_t ldq, float* scale, int hadamard128, void* stream);
+
+/* Exact int32 = a [M,K] (int8) x w [N,K]^T (int8) on the tcgen05 tensor cores.
+ * Replaces torch._int_mm at int8_quant.py:80, :110 (parity / debugging entry). */
+int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw,
+                    int32_t* acc, int64_t ldacc, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Quantised linear from already quantised activations:
+ *   out[m,n] = dequant(sum_k a[m,k] w[n,k]) (+ bias[n])
+ * a_scale fp32 [M]; w_scale fp32 [1] or [N] per w_scale_mode; bias (may be
+ * NULL) [N] in bias_dtype; out [M,N] in out_dtype (I8F_BF16 or I8F_F16).
+ * epilogue_order selects I8F_EPI_PYTORCH (int8_quant.py:84-88, :115-119) or
+ * I8F_EPI_SINGLE (int8_fused_kernel.py:146-173, :302-324).
+ * Replaces _int8_matmul_dequant_kernel / _per_row (int8_fused_kernel.py:91-173, :253-324). */
+int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale,
+                    const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                    const void* bias, int bias_dtype,
+                    void* out, int out_dtype, int64_t ldo,
+                    int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
+
+/* Bytes of caller-owned workspace i8f_linear_forward needs for an [M,K] input. */
+size_t i8f_linear_workspace_bytes(int64_t M, int64_t K);
+
+/* Whole forward of one quantised linear: (rotate) -> per-token quantise ->
+ * int8 GEMM -> dequant (+bias) -> out.  `workspace` holds the int8 activations
+ * and their scales between the two kernels.
+ * Replaces triton_int8_linear / triton_int8_linear_per_row
+ * (int8_fused_kernel.py:179-235, :330-372) and the body of
+ * int8_forward_dynamic[_per_row] (int8_quant.py:67-119). */
+int i8f_linear_forward(const void* x, int x_dtype, int64_t ldx, int hadamard128,
+                       const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                       const void* bias, int bias_dtype,
+                       void* out, int out_dtype, int64_t ldo,
+                       int64_t M, int64_t N, int64_t K, int epilogue_order,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Dynamic-LoRA down projection: t [M,r] = round(x [M,K] @ lora_a [r,K]^T) in
+ * `dtype` (I8F_BF16 or I8F_F16; x, lora_a and t share it), fp32 accumulation.
+ * Replaces F.linear(x_2d, lora_A) at int8_quant.py:768. */
+int i8f_lora_down(const void* x, int64_t ldx, const void* lora_a, int64_t lda,
+                  void* t, int64_t ldt, int dtype, int64_t M, int64_t K, int64_t r, void* stream);
+
+/* Dynamic-LoRA up projection and add: y [M,N] = round(y + round(t [M,r] @ lora_b [N,r]^T)).
+ * Replaces int8_quant.py:769-774. */
+int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb,
+                    void* y, int64_t ldy, int dtype, int64_t M, int64_t N, int64_t r, void* stream);
+
+/* Stochastic-rounding merge of a low-rank update into int8 weights, in place:
+ *   delta = (up [N,r] @ down [r,K]) * lora_scale            (fp32, j ascending)
+ *   hadamard128: delta <- delta rotated per 128-block of K   (fp32)
+ *   d8    = clamp(floor(delta/ws) + [u < frac], -128, 127)
+ *   w     = clamp(int32(w) + d8, -128, 127)
+ * ws = w_scale[0] or w_scale[n] per w_scale_mode.  u comes from `uniforms`
+ * (fp32 [N,K], pitch K) when non-NULL, else from Philox4x32-10 keyed by
+ * `seed` with counter (n, k/4), word k%4, u = (word >> 8) * 2^-24.
+ * factor_dtype is the dtype of up and down.
+ * Replaces reconstruct_lora_diff (plain LoRA, int8_quant.py:139-155),
+ * stochastic_round_int8_delta (:36-62) and the add/clamp at :313-316. */
+int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                      const void* up, int64_t ldup, const void* down, int64_t lddown, int factor_dtype,
+                      int64_t N, int64_t K, int64_t r, float lora_scale, int hadamard128,
+                      const float* uniforms, uint64_t seed, void* stream);
+
+/* Stochastic rounding of an existing fp32 delta (same arithmetic as above
+ * from `delta/ws` on), written to d8 without touching any weight.
+ * Replaces stochastic_round_int8_delta (int8_quant.py:36-62) for callers that
+ * already hold the delta (set_weight, :678-680; LoHa/LoKr deltas). */
+int i8f_stochastic_round(const float* delta, int64_t ldd, const float* w_scale, int w_scale_mode,
+                         int8_t* d8, int64_t ldq, int64_t N, int64_t K,
+                         const float* uniforms, uint64_t seed, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* I8F_H_ */
