@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2] [--impl reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input:
+(Hadamard rotation +) per-token int8 quantisation, the int8 tensor-core GEMM
+and the dequantising epilogue (plus the dynamic-LoRA kernels for c2).  The
+default workload is the QuaRot MLP-up linear (M=4096, K=4096, N=12288).  With
+N > 1 every rank runs its own batch of tokens against replicated weights
+(token-parallel, no data-path collective), so scaling is weak.
+
+Prints ONE JSON line (rank 0).  `value` is aggregate int8 tensor throughput
+with inputs resident in HBM; `e2e` is the same metric through the public
+module call with host buffers (pinned host -> device copy of the activations
+and device -> host copy of the output inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NOMINAL_INT8_TOPS = 4500.0   # B200 dense INT8, data-sheet
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+N_BUFFER_SETS = 4
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:  # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.strip().split(",") for r in Path(self.file.name).read_text().splitlines() if r.strip()]
+        os.unlink(self.file.name)
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                power.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), power_w_max=max(power), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+def workload_shape(name: str):
+    import __graft_entry__ as g
+    wl = g.load_package().workloads
+    key = {"c0": "c0_cpu_linear", "c1": "c1_quarot_mlp_up", "c2": "c2_dynamic_lora"}[name]
+    return wl.CONFIGS[key]
+
+
+def build_cpu_inputs(shape, seed: int, rows: int | None = None):
+    """Seeded CPU tensors of one workload (optionally only the first `rows` tokens)."""
+    import torch
+    import __graft_entry__ as g
+    wl = g.load_package().workloads
+    M = shape.M if rows is None else rows
+    x = wl.activation(M, shape.K, seed=seed)
+    w = wl.weight_fp32(shape.N, shape.K, seed=seed)
+    b = wl.bias_fp32(shape.N, seed=seed) if shape.bias else None
+    lora = wl.lora_factors(shape.N, shape.K, shape.lora_rank, seed=seed) if shape.lora_rank else None
+    return x, w, b, lora
+
+
+def config_dict(shape, world: int):
+    working_set_mb = N_BUFFER_SETS * (shape.M * shape.K * 3 + shape.N * shape.K + shape.M * shape.N * 2) / 1e6
+    return {"workload": shape.name, "M_per_gpu": shape.M, "K": shape.K, "N": shape.N, "hadamard": shape.hadamard,
+            "weight_scale": "per_channel" if shape.per_channel else "tensorwise", "bias": shape.bias,
+            "lora_rank": shape.lora_rank, "out_dtype": "bf16", "parallelism": f"token-parallel x{world}",
+            "l2": f"inputs rotate over {N_BUFFER_SETS} buffer sets ({working_set_mb:.0f} MB > 126 MB L2)"}
+
+
+# ----------------------------------------------------------------- CPU arm
+def cpu_reference_rate(shape, steps: int, warmup: int, budget_s: float):
+    """Times the oracle's CPU PyTorch path (what the reference runs without a GPU) on a bounded sample."""
+    import torch
+    from oracle import torch_path as tp
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rows = min(shape.M, 512)
+    x, w, b, lora = build_cpu_inputs(shape, seed=0, rows=rows)
+    if shape.hadamard:
+        w = tp.rotate_weight(w)
+    wq, ws = tp.quantize_rowwise(w) if shape.per_channel else tp.quantize_tensorwise(w)
+
+    def step():
+        y = tp.linear_w8a8(x, wq, ws, b, torch.bfloat16, hadamard=shape.hadamard)
+        if lora is not None:
+            y = tp.lora_dynamic_add(y, x, lora[0], lora[1])
+        return y
+
+    t0 = time.perf_counter()
+    step()
+    first = time.perf_counter() - t0
+    for _ in range(max(0, warmup - 1)):
+        step()
+    n = max(1, min(steps, int(budget_s / max(first, 1e-4))))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        step()
+    dt = (time.perf_counter() - t0) / n
+    ops = 2.0 * rows * shape.N * shape.K
+    return {"value": ops / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+            "sample": f"first {rows} of {shape.M} tokens of {shape.name}, {n} timed passes of "
+                      f"{dt * 1e3:.2f} ms, torch {torch.get_num_threads()} threads"}, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    shape = workload_shape(args.workload)
+    base, dt = cpu_reference_rate(shape, args.steps, args.warmup, budget_s=60.0)
+    line = {
+        "impl": "reference", "metric": "w8a8_linear_int8_throughput", "value": base["value"], "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": config_dict(shape, max(1, args.gpus)),
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------- GPU arm
+def run_gpu_arm(args):
+    import torch
+    import __graft_entry__ as g
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = g.load_package()
+    F, nat = pkg.functional, pkg._native
+    nat.require_device(dev)
+    shape = workload_shape(args.workload)
+    M, K, N = shape.M, shape.K, shape.N
+    out_dtype = torch.bfloat16
+
+    # Weak scaling: rank r owns its own batch of M tokens (seed differs per rank), weights replicated.
+    sets = []
+    for i in range(N_BUFFER_SETS):
+        x, w, b, lora = build_cpu_inputs(shape, seed=100 * rank + i)
+        wd = w.to(dev)
+        if shape.per_channel:
+            wq, ws = F.quantize_weight_rows(wd, hadamard=shape.hadamard)
+        else:
+            wq, ws = F.quantize_tensorwise(wd, hadamard=shape.hadamard)
+            ws = ws.reshape(1)
+        del wd
+        sets.append({"x": x.to(dev), "x_host": x.pin_memory(), "wq": wq, "ws": ws,
+                     "bias": None if b is None else b.to(dev).to(out_dtype),
+                     "lora": None if lora is None else (lora[0].to(dev), lora[1].to(dev)),
+                     "y_host": torch.empty((M, N), dtype=out_dtype).pin_memory()})
+    gemm_events = []
+
+    def step(i: int, timed: bool):
+        s = sets[i % N_BUFFER_SETS]
+        q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype)
+        if timed:
+            e1.record()
+            gemm_events.append((e0, e1))
+        if s["lora"] is not None:
+            t = F.lora_down(s["x"], s["lora"][0])
+            F.lora_up_add_(y, t, s["lora"][1])
+        return y
+
+    launches_per_step = 2 + (2 if shape.lora_rank else 0)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i, False)
+    sync_all()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.15)
+    sync_all()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        step(i, True)
+    t_end.record()
+    sync_all()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if sampler else None
+    gemm_ms = sorted(a.elapsed_time(b) for a, b in gemm_events)
+    gemm_avg_ms = sum(gemm_ms) / len(gemm_ms)
+
+    # end-to-end: host buffers through the public forward call, copies inside the timed region
+    def e2e_step(i: int):
+        s = sets[i % N_BUFFER_SETS]
+        xd = s["x_host"].to(dev, non_blocking=True)
+        y = F.linear_forward(xd, s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard)
+        if s["lora"] is not None:
+            F.lora_up_add_(y, F.lora_down(xd, s["lora"][0]), s["lora"][1])
+        s["y_host"].copy_(y, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(3):
+        e2e_step(i)
+    sync_all()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e_end.record()
+    sync_all()
+    e2e_ms = e_start.elapsed_time(e_end)
+    status = nat.device_status()
+
+    if dist is not None:
+        t = torch.tensor([elapsed_ms, e2e_ms, gemm_avg_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms, gemm_avg_ms = (float(v) for v in t.tolist())
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    ops_step = 2.0 * M * N * K                       # int8 GEMM ops of one rank's step
+    value = world * ops_step * args.steps / (elapsed_ms * 1e-3) / 1e12
+    e2e_value = world * ops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    peaks, peak_kind = measured_peaks()
+    # int8 tensor throughput is twice the bf16 rate of the same tensor cores; the steps run back to
+    # back for a short burst, so the burst figure is the denominator
+    peak_tops = 2.0 * peaks["bf16_tflops"]
+    achieved = ops_step / (gemm_avg_ms * 1e-3) / 1e12
+    cpu_base, _ = cpu_reference_rate(shape, steps=20, warmup=2, budget_s=12.0)
+    line = {
+        "metric": "w8a8_linear_int8_throughput", "value": value, "unit": "TOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": config_dict(shape, world),
+        "frac_of_nominal_int8_peak": value / (world * NOMINAL_INT8_TOPS),
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8,256>", "achieved": achieved, "peak": peak_tops,
+                     "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": None,
+                     "peak_source": f"2 x bf16_tflops (burst) of {peak_kind} MEASURED_PEAKS.json; int8 ops counted as 2*M*N*K",
+                     "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "kernel_ms_avg": gemm_avg_ms,
+                     "kernel_ms_best": gemm_ms[0]},
+        "cpu_baseline": cpu_base,
+        "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "device_status": status,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", choices=["c0", "c1", "c2"], default="c1")
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -175,7 +175,8 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
 #pragma unroll
             for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
         // reduce over the lanes of this row that share a warp
-        const int span = tpr < 32 ? tpr : 32;
+        // (the whole warp when only the tensor-wide maximum is wanted)
+        const int span = (MODE == kAbsmaxOnly || tpr > 32) ? 32 : tpr;
         for (int d = 1; d < span; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
         if (tpr > 32 || MODE == kAbsmaxOnly) {
             if (lane == 0) s_part[threadIdx.x >> 5] = amax;

@@ -1,0 +1,224 @@
+"""Tensor-level wrappers over the C ABI (one call per kernel).
+
+All functions take CUDA tensors on one sm_100 device, run on the current
+stream of that device, never synchronise and never fall back to another
+implementation.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _native as nat
+
+HADAMARD_GROUP = 128
+
+
+def _rows(t: Tensor) -> Tensor:
+    """2-D view with unit inner stride (copies only if the layout forces it)."""
+    if t.dim() != 2:
+        raise ValueError(f"expected a 2-D tensor, got shape {tuple(t.shape)}")
+    if t.stride(1) != 1 and t.shape[1] > 1:
+        t = t.contiguous()
+    if t.shape[0] > 1 and t.stride(0) < t.shape[1]:
+        t = t.contiguous()
+    return t
+
+
+def _ld(t: Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], 1)
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return nat.DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dtype}; expected bf16, fp16 or fp32") from None
+
+
+def _wscale_arg(w_scale, device: torch.device) -> tuple[Tensor, int]:
+    """Device fp32 tensor + granularity code from a float, 0-d/1-element tensor or [N,1]/[N] tensor."""
+    if not isinstance(w_scale, Tensor):
+        return torch.tensor([float(w_scale)], dtype=torch.float32, device=device), nat.WSCALE_TENSOR
+    ws = w_scale.to(device=device, dtype=torch.float32)
+    if ws.numel() == 1:
+        return ws.reshape(1), nat.WSCALE_TENSOR
+    return ws.reshape(-1).contiguous(), nat.WSCALE_CHANNEL
+
+
+def quantize_rowwise(x: Tensor, hadamard: bool = False, return_rotated: bool = False):
+    """Per-token absmax int8 quantisation, optionally after the 128-block Hadamard rotation.
+
+    Returns (q int8 [M,K], scale fp32 [M,1]) and, if asked, the rotated activations in x's dtype.
+    """
+    nat.require_device(x.device)
+    x = _rows(x)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scale = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    xrot = torch.empty_like(x, memory_format=torch.contiguous_format) if (hadamard and return_rotated) else None
+    if xrot is not None and _ld(x) != K:
+        x = x.contiguous()
+    if M > 0:
+        nat.check(nat.load().i8f_quant_rowwise(nat.ptr(x), _code(x.dtype), M, K, _ld(x), nat.ptr(q), K, nat.ptr(scale),
+                                               1 if hadamard else 0, nat.ptr(xrot), nat.current_stream(x.device)),
+                  "i8f_quant_rowwise")
+    if return_rotated:
+        return q, scale, (xrot if hadamard else x)
+    return q, scale
+
+
+def quantize_weight_rows(w: Tensor, hadamard: bool = False):
+    """Per-output-channel weight quantisation in fp32 (rotation, if any, also in fp32)."""
+    nat.require_device(w.device)
+    w = _rows(w)
+    N, K = w.shape
+    q = torch.empty((N, K), dtype=torch.int8, device=w.device)
+    scale = torch.empty((N, 1), dtype=torch.float32, device=w.device)
+    if N > 0:
+        nat.check(nat.load().i8f_quant_weight_rows(nat.ptr(w), _code(w.dtype), N, K, _ld(w), nat.ptr(q), K, nat.ptr(scale),
+                                                   1 if hadamard else 0, nat.current_stream(w.device)),
+                  "i8f_quant_weight_rows")
+    return q, scale
+
+
+def quantize_tensorwise(w: Tensor, hadamard: bool = False):
+    """One-scale quantisation of a whole matrix; returns (q int8, 0-d fp32 scale tensor)."""
+    nat.require_device(w.device)
+    w = _rows(w)
+    N, K = w.shape
+    q = torch.empty((N, K), dtype=torch.int8, device=w.device)
+    scale = torch.empty((1,), dtype=torch.float32, device=w.device)
+    scratch = torch.empty((1,), dtype=torch.float32, device=w.device)
+    nat.check(nat.load().i8f_quant_tensorwise(nat.ptr(w), _code(w.dtype), N, K, _ld(w), nat.ptr(q), K, nat.ptr(scale),
+                                              1 if hadamard else 0, nat.ptr(scratch), nat.current_stream(w.device)),
+              "i8f_quant_tensorwise")
+    return q, scale.reshape(())
+
+
+def gemm_i8_i32(a: Tensor, w: Tensor) -> Tensor:
+    """Exact int32 [M,N] = a int8 [M,K] @ w int8 [N,K]^T."""
+    nat.require_device(a.device)
+    a, w = _rows(a), _rows(w)
+    (M, K), (N, K2) = a.shape, w.shape
+    if K != K2 or a.dtype != torch.int8 or w.dtype != torch.int8:
+        raise ValueError("gemm_i8_i32 expects int8 [M,K] and int8 [N,K]")
+    acc = torch.empty((M, N), dtype=torch.int32, device=a.device)
+    if M and N:
+        nat.check(nat.load().i8f_gemm_i8_i32(nat.ptr(a), _ld(a), nat.ptr(w), _ld(w), nat.ptr(acc), N, M, N, K,
+                                             nat.current_stream(a.device)), "i8f_gemm_i8_i32")
+    return acc
+
+
+def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype,
+                order: int = nat.EPI_PYTORCH) -> Tensor:
+    """Dequantising int8 GEMM from pre-quantised activations."""
+    nat.require_device(q.device)
+    q, w = _rows(q), _rows(w)
+    M, K = q.shape
+    N = w.shape[0]
+    ws, mode = _wscale_arg(w_scale, q.device)
+    if mode == nat.WSCALE_CHANNEL and ws.numel() != N:
+        raise ValueError(f"per-channel weight scale has {ws.numel()} entries for N={N}")
+    if bias is not None:
+        bias = bias.to(q.device).contiguous()
+    out = torch.empty((M, N), dtype=out_dtype, device=q.device)
+    if M and N:
+        nat.check(nat.load().i8f_linear_w8a8(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w),
+                                             nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                             nat.ptr(out), _code(out_dtype), N, M, N, K, order,
+                                             nat.current_stream(q.device)), "i8f_linear_w8a8")
+    return out
+
+
+def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype, hadamard: bool = False,
+                   order: int = nat.EPI_PYTORCH, workspace: Tensor | None = None) -> Tensor:
+    """(rotate) -> quantise -> int8 GEMM -> dequant (+bias) through the single fused entry point."""
+    nat.require_device(x.device)
+    x, w = _rows(x), _rows(w)
+    M, K = x.shape
+    N = w.shape[0]
+    ws, mode = _wscale_arg(w_scale, x.device)
+    if bias is not None:
+        bias = bias.to(x.device).contiguous()
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if M == 0 or N == 0:
+        return out
+    need = nat.load().i8f_linear_workspace_bytes(M, K)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
+    nat.check(nat.load().i8f_linear_forward(nat.ptr(x), _code(x.dtype), _ld(x), 1 if hadamard else 0, nat.ptr(w), _ld(w),
+                                            nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                            nat.ptr(out), _code(out_dtype), N, M, N, K, order, nat.ptr(workspace),
+                                            workspace.numel() * workspace.element_size(), nat.current_stream(x.device)),
+              "i8f_linear_forward")
+    return out
+
+
+def lora_down(x: Tensor, lora_a: Tensor) -> Tensor:
+    """t [M,r] = x [M,K] @ lora_a [r,K]^T, rounded to x's dtype (bf16 or fp16)."""
+    nat.require_device(x.device)
+    x, lora_a = _rows(x), _rows(lora_a.to(x.dtype))
+    M, K = x.shape
+    r = lora_a.shape[0]
+    t = torch.empty((M, r), dtype=x.dtype, device=x.device)
+    if M and r:
+        nat.check(nat.load().i8f_lora_down(nat.ptr(x), _ld(x), nat.ptr(lora_a), _ld(lora_a), nat.ptr(t), r, _code(x.dtype),
+                                           M, K, r, nat.current_stream(x.device)), "i8f_lora_down")
+    return t
+
+
+def lora_up_add_(y: Tensor, t: Tensor, lora_b: Tensor) -> Tensor:
+    """In place y [M,N] += round(t [M,r] @ lora_b [N,r]^T) with the reference's two roundings."""
+    nat.require_device(y.device)
+    if y.dim() != 2 or y.stride(1) != 1:
+        raise ValueError("y must be a 2-D tensor with unit inner stride")
+    t, lora_b = _rows(t), _rows(lora_b.to(y.dtype))
+    M, N = y.shape
+    r = t.shape[1]
+    if M and N and r:
+        nat.check(nat.load().i8f_lora_up_add(nat.ptr(t), _ld(t), nat.ptr(lora_b), _ld(lora_b), nat.ptr(y), _ld(y),
+                                             _code(y.dtype), M, N, r, nat.current_stream(y.device)), "i8f_lora_up_add")
+    return y
+
+
+def lora_merge_sr_(w: Tensor, w_scale, up: Tensor, down: Tensor, lora_scale: float, hadamard: bool = False,
+                   uniforms: Tensor | None = None, seed: int = 0) -> Tensor:
+    """In place stochastic-rounding merge of (up @ down) * lora_scale into int8 weights."""
+    nat.require_device(w.device)
+    if w.dtype != torch.int8 or w.dim() != 2 or w.stride(1) != 1:
+        raise ValueError("w must be a 2-D int8 tensor with unit inner stride")
+    N, K = w.shape
+    up = _rows(up.reshape(up.shape[0], -1).to(w.device))
+    down = _rows(down.reshape(down.shape[0], -1).to(w.device))
+    if up.dtype != down.dtype:
+        down = down.to(up.dtype)
+    r = up.shape[1]
+    if up.shape[0] != N or down.shape != (r, K):
+        raise ValueError(f"factor shapes {tuple(up.shape)} x {tuple(down.shape)} do not give [{N},{K}]")
+    ws, mode = _wscale_arg(w_scale, w.device)
+    if uniforms is not None:
+        uniforms = uniforms.to(device=w.device, dtype=torch.float32).contiguous()
+        if uniforms.shape != (N, K):
+            raise ValueError("uniforms must have the shape of w")
+    nat.check(nat.load().i8f_lora_merge_sr(nat.ptr(w), _ld(w), nat.ptr(ws), mode, nat.ptr(up), _ld(up), nat.ptr(down),
+                                           _ld(down), _code(up.dtype), N, K, r, float(lora_scale), 1 if hadamard else 0,
+                                           nat.ptr(uniforms), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                                           nat.current_stream(w.device)), "i8f_lora_merge_sr")
+    return w
+
+
+def stochastic_round(delta: Tensor, w_scale, uniforms: Tensor | None = None, seed: int = 0) -> Tensor:
+    """int8 = clamp(floor(delta/scale) + [u < frac]) for an fp32 [N,K] delta."""
+    nat.require_device(delta.device)
+    delta = _rows(delta.float())
+    N, K = delta.shape
+    ws, mode = _wscale_arg(w_scale, delta.device)
+    out = torch.empty((N, K), dtype=torch.int8, device=delta.device)
+    if uniforms is not None:
+        uniforms = uniforms.to(device=delta.device, dtype=torch.float32).contiguous()
+    if N and K:
+        nat.check(nat.load().i8f_stochastic_round(nat.ptr(delta), _ld(delta), nat.ptr(ws), mode, nat.ptr(out), K, N, K,
+                                                  nat.ptr(uniforms), int(seed) & 0xFFFFFFFFFFFFFFFF,
+                                                  nat.current_stream(delta.device)), "i8f_stochastic_round")
+    return out

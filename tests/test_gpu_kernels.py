@@ -1,0 +1,335 @@
+"""Parity of every CUDA kernel with the CPU oracle, through the C ABI, on a B200.
+
+Bars: int8 activations / weights, fp32 scales and int32 accumulators are
+bit-exact; bf16 / fp16 outputs are within 1e-2 * RMS(reference output) in
+max-abs (they are in fact bit-exact for the plain linear, where no
+accumulation order is involved after the exact integer GEMM).
+"""
+import hashlib
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bitspec as bs
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+NAME = {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}
+
+
+def rms(a):
+    return float(np.sqrt(np.mean(np.asarray(a, dtype=np.float64) ** 2)))
+
+
+def to_np(t):
+    return t.detach().float().cpu().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
+
+
+def dev_ws(ws):
+    return torch.from_numpy(np.asarray(ws, dtype=np.float32)).to(DEV)
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(cuda_pkg):
+    yield
+    torch.cuda.synchronize()
+    assert cuda_pkg._native.device_status() == 0, "a bounded device-side wait ran out"
+
+
+# ------------------------------------------------------------------ K1 quant
+@pytest.mark.parametrize("M,K,had,dt", [
+    (200, 512, False, torch.bfloat16), (256, 3072, False, torch.bfloat16), (64, 4096, True, torch.bfloat16),
+    (33, 12288, True, torch.bfloat16), (70, 1024, False, torch.float16), (70, 1024, True, torch.float16),
+    (70, 1024, True, torch.float32), (5, 16384, False, torch.bfloat16), (300, 128, True, torch.bfloat16),
+    (1, 8, False, torch.bfloat16), (17, 24, False, torch.float32), (3, 32768, True, torch.bfloat16),
+])
+def test_quant_rowwise_bit_exact(cuda_pkg, M, K, had, dt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=3, dtype=dt)
+    xr = bs.rotate_activation(to_np(x), NAME[dt]) if had else to_np(x)
+    q_want, s_want = bs.quantize_rowwise(xr)
+    q, s, xrot = F.quantize_rowwise(x.to(DEV), hadamard=had, return_rotated=True)
+    assert np.array_equal(to_np(q), q_want)
+    assert np.array_equal(to_np(s), s_want)
+    if had:
+        assert np.array_equal(to_np(xrot), xr)
+
+
+def test_quant_edge_rows(cuda_pkg):
+    """All-zero rows take the 1e-30 floor; a strided (pitched) input is read in place."""
+    F = cuda_pkg.functional
+    x = torch.zeros(6, 256, dtype=torch.bfloat16)
+    x[1, 5] = -3.0
+    x[2] = 1e-38
+    x[3, 200] = 65280.0
+    q_want, s_want = bs.quantize_rowwise(to_np(x))
+    q, s = F.quantize_rowwise(x.to(DEV))
+    assert np.array_equal(to_np(q), q_want) and np.array_equal(to_np(s), s_want)
+    assert to_np(s)[0, 0] == np.float32(1e-30)
+    big = torch.randn(10, 512, dtype=torch.bfloat16, generator=torch.Generator().manual_seed(1)).to(DEV)
+    view = big[:, 128:384]
+    q, s = F.quantize_rowwise(view)
+    q_want, s_want = bs.quantize_rowwise(to_np(view))
+    assert np.array_equal(to_np(q), q_want) and np.array_equal(to_np(s), s_want)
+    q, s = F.quantize_rowwise(torch.empty(0, 64, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (0, 64) and s.shape == (0, 1)
+
+
+def test_quant_golden_fixture(cuda_pkg, golden):
+    g = golden("linear_small.npz")
+    x = torch.from_numpy(g["x_bits"].view(np.int16)).view(torch.bfloat16).to(DEV)
+    q, s = cuda_pkg.functional.quantize_rowwise(x)
+    assert np.array_equal(to_np(q), g["xq"]) and np.array_equal(to_np(s), g["xs"])
+
+
+@pytest.mark.parametrize("N,K,had,dt", [(300, 512, False, torch.float32), (300, 512, True, torch.float32),
+                                        (128, 4096, True, torch.bfloat16), (77, 1152, False, torch.float16)])
+def test_weight_quant_bit_exact(cuda_pkg, N, K, had, dt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    w = wl.weight_fp32(N, K, seed=13).to(dt)
+    wr = bs.rotate_weight(to_np(w)) if had else to_np(w)
+    q_want, s_want = bs.quantize_rowwise(wr)
+    q, s = F.quantize_weight_rows(w.to(DEV), hadamard=had)
+    assert np.array_equal(to_np(q), q_want) and np.array_equal(to_np(s), s_want)
+    qt_want, st_want = bs.quantize_tensorwise(wr)
+    qt, st = F.quantize_tensorwise(w.to(DEV), hadamard=had)
+    assert np.array_equal(to_np(qt), qt_want) and float(st.item()) == float(st_want)
+
+
+# ------------------------------------------------------------------ K2 GEMM
+@pytest.mark.parametrize("M,N,K", [
+    (128, 256, 128), (128, 256, 4096), (256, 512, 1024), (1024, 2048, 512), (200, 328, 528), (17, 40, 16),
+    (1, 8, 64), (129, 100, 144), (300, 64, 272), (16, 16, 16), (4608, 300, 192), (2048, 12288, 256),
+])
+def test_gemm_int32_bit_exact(cuda_pkg, M, N, K):
+    gen = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    a = torch.randint(-128, 128, (M, K), generator=gen, dtype=torch.int8)
+    w = torch.randint(-128, 128, (N, K), generator=gen, dtype=torch.int8)
+    want = bs.int_mm(a.numpy(), w.numpy())
+    got = cuda_pkg.functional.gemm_i8_i32(a.to(DEV), w.to(DEV))
+    assert np.array_equal(to_np(got), want)
+
+
+def test_gemm_extreme_values_do_not_saturate(cuda_pkg):
+    """-128 * -128 * K stays exact (the MMA must not saturate)."""
+    K = 8192
+    a = torch.full((130, K), -128, dtype=torch.int8)
+    w = torch.full((70, K), -128, dtype=torch.int8)
+    w[1] = 127
+    got = to_np(cuda_pkg.functional.gemm_i8_i32(a.to(DEV), w.to(DEV)))
+    assert np.all(got[:, 0] == 128 * 128 * K) and np.all(got[:, 1] == -128 * 127 * K)
+
+
+def test_gemm_linearity_at_full_size(cuda_pkg):
+    """Size-independent property at the benchmark shape: (A1 + A2) W^T == A1 W^T + A2 W^T, and a
+    column checksum against int64 arithmetic."""
+    M, K, N = 4096, 4096, 12288
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    a1 = torch.randint(-60, 61, (M, K), generator=gen, dtype=torch.int8, device=DEV)
+    a2 = torch.randint(-60, 61, (M, K), generator=gen, dtype=torch.int8, device=DEV)
+    w = torch.randint(-128, 128, (N, K), generator=gen, dtype=torch.int8, device=DEV)
+    F = cuda_pkg.functional
+    c1, c2, c12 = F.gemm_i8_i32(a1, w), F.gemm_i8_i32(a2, w), F.gemm_i8_i32(a1 + a2, w)
+    assert torch.equal(c1 + c2, c12)
+    # sum over rows of C equals (sum over rows of A) W^T, computed in float64 on the device
+    want = a1.to(torch.float64).sum(0) @ w.to(torch.float64).T
+    assert torch.equal(c1.to(torch.float64).sum(0), want)
+
+
+# ------------------------------------------------------ K2 + epilogue (linear)
+@pytest.mark.parametrize("M,K,N,per_ch,use_bias,had,order,dt", [
+    (256, 3072, 3072, True, True, False, 0, torch.bfloat16),
+    (200, 512, 328, False, True, False, 0, torch.bfloat16),
+    (200, 512, 328, True, False, True, 0, torch.bfloat16),
+    (130, 256, 520, False, True, True, 1, torch.bfloat16),
+    (130, 256, 520, True, True, False, 1, torch.bfloat16),
+    (64, 384, 200, True, True, False, 0, torch.float16),
+    (17, 128, 72, False, False, False, 0, torch.float16),
+    (90, 640, 77, True, True, False, 0, torch.bfloat16),     # N not a multiple of 8: scalar store path
+])
+def test_linear_forward_matches_oracle(cuda_pkg, M, K, N, per_ch, use_bias, had, order, dt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=5, dtype=dt)
+    w = wl.weight_fp32(N, K, seed=5)
+    b = wl.bias_fp32(N, seed=5) if use_bias else None
+    wn = bs.rotate_weight(w.numpy()) if had else w.numpy()
+    wq, ws = bs.quantize_rowwise(wn) if per_ch else bs.quantize_tensorwise(wn)
+    want = bs.linear_w8a8(to_np(x), wq, ws, None if b is None else b.numpy(), act_dtype=NAME[dt], hadamard=had,
+                          order="pytorch" if order == 0 else "single")
+    y = F.linear_forward(x.to(DEV), torch.from_numpy(wq).to(DEV), dev_ws(ws), None if b is None else b.to(DEV), dt,
+                         hadamard=had, order=order)
+    got = to_np(y)
+    assert np.max(np.abs(got - want)) <= TOL * rms(want)
+    assert np.array_equal(got, want), "the epilogue is deterministic fp32 arithmetic and should be bit-exact"
+
+
+def test_linear_golden_fixtures(cuda_pkg, golden):
+    """Outputs recorded from the reference's int8_forward_dynamic[_per_row] on CPU."""
+    F = cuda_pkg.functional
+    g = golden("linear_small.npz")
+    x = torch.from_numpy(g["x_bits"].view(np.int16)).view(torch.bfloat16).to(DEV)
+    b = torch.from_numpy(g["bias"]).to(DEV)
+    acc = F.gemm_i8_i32(torch.from_numpy(g["xq"]).to(DEV), torch.from_numpy(g["wq_c"]).to(DEV))
+    assert np.array_equal(to_np(acc), g["acc_c"])
+    y = F.linear_forward(x, torch.from_numpy(g["wq_c"]).to(DEV), dev_ws(g["ws_c"]), b, torch.bfloat16)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), g["y_c_bits"])
+    y = F.linear_forward(x, torch.from_numpy(g["wq_c"]).to(DEV), dev_ws(g["ws_c"]), None, torch.bfloat16)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), g["y_c_nb_bits"])
+    y = F.linear_forward(x, torch.from_numpy(g["wq_t"]).to(DEV), float(g["ws_t"]), b, torch.bfloat16)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), g["y_t_bits"])
+    y = F.linear_forward(x.half(), torch.from_numpy(g["wq_t"]).to(DEV), float(g["ws_t"]), b, torch.float16)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), g["y_t_f16_bits"])
+
+
+def test_config0_digests_on_gpu(cuda_pkg):
+    """The CPU-runnable benchmark configuration at full size against the reference's recorded digests."""
+    ref = json.loads((GOLDEN / "config0_digests.json").read_text())
+    M, K, N = ref["shape"]
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=ref["seed"]).to(DEV)
+    w = wl.weight_fp32(N, K, seed=ref["seed"]).to(DEV)
+    b = wl.bias_fp32(N, seed=ref["seed"]).to(DEV)
+    sha = lambda t: hashlib.sha256(np.ascontiguousarray(t.cpu().numpy()).tobytes()).hexdigest()  # noqa: E731
+    wq, ws = F.quantize_weight_rows(w)
+    assert sha(wq) == ref["wq"] and sha(ws) == ref["ws"]
+    q, s = F.quantize_rowwise(x)
+    assert sha(q) == ref["xq"] and sha(s) == ref["xs"]
+    assert sha(F.gemm_i8_i32(q, wq)) == ref["acc"]
+    y = F.linear_forward(x, wq, ws, b, torch.bfloat16)
+    assert sha(y.view(torch.int16)) == ref["y_bits"]
+
+
+def test_quarot_golden_within_rotation_tolerance(cuda_pkg, golden):
+    """Against the reference's library-matmul rotation: a few last-place differences are expected."""
+    F = cuda_pkg.functional
+    g = golden("quarot_small.npz")
+    x = torch.from_numpy(g["x_bits"].view(np.int16)).view(torch.bfloat16).to(DEV)
+    q, s, xr = F.quantize_rowwise(x, hadamard=True, return_rotated=True)
+    ref = bs.bf16_bits_to_f32(g["xr_bits"])
+    assert (to_np(xr) != ref).mean() <= 1e-3
+    assert (to_np(q) != g["xrq"]).mean() <= 1e-4 and np.array_equal(to_np(s), g["xrs"])
+    y = F.linear_forward(x, torch.from_numpy(g["wrq"]).to(DEV), dev_ws(g["wrs"]), None, torch.bfloat16, hadamard=True)
+    want = bs.bf16_bits_to_f32(g["y_rot_bits"])
+    assert np.max(np.abs(to_np(y) - want)) <= TOL * rms(want)
+
+
+def test_split_calls_equal_fused_call(cuda_pkg):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(300, 1024, seed=8).to(DEV)
+    wq, ws = F.quantize_weight_rows(wl.weight_fp32(520, 1024, seed=8).to(DEV))
+    b = wl.bias_fp32(520, seed=8).to(DEV)
+    q, s = F.quantize_rowwise(x)
+    y1 = F.linear_w8a8(q, s, wq, ws, b, torch.bfloat16)
+    y2 = F.linear_forward(x, wq, ws, b, torch.bfloat16)
+    assert torch.equal(y1, y2)
+
+
+# ------------------------------------------------------------ K3 dynamic LoRA
+@pytest.mark.parametrize("M,K,N,r,dt", [(256, 512, 384, 64, torch.bfloat16), (200, 1024, 328, 16, torch.bfloat16),
+                                        (130, 256, 520, 8, torch.bfloat16), (96, 384, 160, 32, torch.float16),
+                                        (300, 512, 264, 136, torch.bfloat16)])
+def test_dynamic_lora_matches_oracle(cuda_pkg, M, K, N, r, dt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=9, dtype=dt)
+    A, B = wl.lora_factors(N, K, r, seed=9, dtype=dt)
+    y0 = torch.randn(M, N, generator=torch.Generator().manual_seed(4)).to(dt)
+    t_want = bs.lora_down(to_np(x), to_np(A), NAME[dt])
+    t = F.lora_down(x.to(DEV), A.to(DEV))
+    assert np.max(np.abs(to_np(t) - t_want)) <= TOL * rms(t_want)
+    y_want = bs.lora_up_add(to_np(y0), to_np(t), to_np(B), NAME[dt])
+    y = y0.to(DEV).clone()
+    F.lora_up_add_(y, t, B.to(DEV))
+    assert np.max(np.abs(to_np(y) - y_want)) <= TOL * rms(y_want)
+
+
+def test_module_golden_with_dynamic_lora(cuda_pkg, golden):
+    """Output of the reference's Linear.forward with lora_A / lora_B set (CPU run)."""
+    F = cuda_pkg.functional
+    g = golden("module_small.npz")
+    as_bf16 = lambda bits: torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).to(DEV)  # noqa: E731
+    x = as_bf16(g["x_bits"])
+    y = F.linear_forward(x, torch.from_numpy(g["wq"]).to(DEV), dev_ws(g["ws"]), as_bf16(g["bias_bits"]), torch.bfloat16)
+    assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), g["y_bits"])
+    F.lora_up_add_(y, F.lora_down(x, as_bf16(g["lora_a_bits"])), as_bf16(g["lora_b_bits"]))
+    want = bs.bf16_bits_to_f32(g["y_lora_bits"])
+    assert np.max(np.abs(to_np(y) - want)) <= TOL * rms(want)
+
+
+# ------------------------------------------------------ K4 stochastic merge
+@pytest.mark.parametrize("N,K,r,per_ch,had,philox,fdt", [
+    (256, 512, 64, True, False, False, torch.bfloat16), (200, 384, 16, False, True, False, torch.bfloat16),
+    (100, 200, 8, True, False, True, torch.float32), (512, 1024, 64, True, True, True, torch.float16),
+    (33, 130, 4, False, False, True, torch.bfloat16), (64, 256, 0, True, False, False, torch.bfloat16),
+])
+def test_lora_merge_bit_exact(cuda_pkg, N, K, r, per_ch, had, philox, fdt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    w = wl.weight_fp32(N, K, seed=11)
+    wq, ws = bs.quantize_rowwise(w.numpy()) if per_ch else bs.quantize_tensorwise(w.numpy())
+    down, up = wl.lora_factors(N, K, max(r, 1), seed=11, dtype=fdt)
+    down, up = down[:r], (up[:, :r].float() * 30).to(fdt)
+    u = bs.philox_uniforms(318008, N, K) if philox else wl.uniforms(N, K, seed=11).numpy()
+    want = bs.lora_merge(wq, ws, to_np(up), to_np(down), 0.75, u, hadamard=had)
+    wd = torch.from_numpy(wq).to(DEV).clone()
+    F.lora_merge_sr_(wd, dev_ws(ws), up.to(DEV), down.to(DEV), 0.75, hadamard=had,
+                     uniforms=None if philox else torch.from_numpy(u).to(DEV), seed=318008)
+    assert np.array_equal(to_np(wd), want)
+    if r:
+        assert (want != wq).mean() > 0.5, "the case must actually change the weights"
+    else:
+        assert np.array_equal(want, wq)
+
+
+def test_merge_golden_fixture(cuda_pkg, golden):
+    """Weights produced by the reference's INT8LoRAPatchAdapter.calculate_weight on CPU (uniforms recorded)."""
+    F = cuda_pkg.functional
+    g = golden("sr_merge_small.npz")
+    as_bf16 = lambda bits: torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).to(DEV)  # noqa: E731
+    up, down, u = as_bf16(g["up_bits"]), as_bf16(g["down_bits"]), torch.from_numpy(g["u"]).to(DEV)
+    for wq, ws, merged in ((g["wq_c"], g["ws_c"], g["merged_c"]), (g["wq_t"], g["ws_t"], g["merged_t"])):
+        wd = torch.from_numpy(wq).to(DEV).clone()
+        F.lora_merge_sr_(wd, dev_ws(ws), up, down, 0.5, uniforms=u)
+        assert np.array_equal(to_np(wd), merged)
+    sr = F.stochastic_round(torch.from_numpy(g["delta"]).to(DEV), dev_ws(g["ws_c"]), uniforms=u)
+    assert np.array_equal(to_np(sr), g["sr_c"])
+    wd = torch.from_numpy(g["wrq"]).to(DEV).clone()
+    F.lora_merge_sr_(wd, dev_ws(g["wrs"]), up, down, 0.5, hadamard=True, uniforms=u)
+    assert np.max(np.abs(to_np(wd).astype(int) - g["merged_rot"].astype(int))) <= 1
+    assert (to_np(wd) != g["merged_rot"]).mean() <= 1e-3
+
+
+def test_stochastic_rounding_is_unbiased_in_philox_mode(cuda_pkg):
+    """E[q * s] == x within 4 sigma and P(round up) == frac, with the in-kernel counter RNG."""
+    F = cuda_pkg.functional
+    N, K = 512, 2048
+    delta = torch.full((N, K), 0.3 * 0.01, device=DEV)
+    q = F.stochastic_round(delta, 0.01, seed=1234).float()
+    p_up = float((q == 1).float().mean())
+    assert set(torch.unique(q).tolist()) <= {0.0, 1.0}
+    assert abs(p_up - 0.3) < 4 * (0.3 * 0.7 / (N * K)) ** 0.5 + 1e-6
+    q2 = F.stochastic_round(delta, 0.01, seed=1235).float()
+    assert not torch.equal(q, q2)
+    assert torch.equal(q, F.stochastic_round(delta, 0.01, seed=1234).float())
+
+
+def test_merge_idempotent_shape_properties_at_full_size(cuda_pkg):
+    """Config-2 size: a zero-strength merge leaves W untouched; merging +D then -D with the same
+    uniforms restores every weight that did not clamp to within one step."""
+    F = cuda_pkg.functional
+    N = K = 4096
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    w0 = torch.randint(-100, 101, (N, K), generator=gen, dtype=torch.int8, device=DEV)
+    ws = torch.rand(N, 1, generator=gen, device=DEV) * 1e-3 + 5e-4
+    up = (torch.randn(N, 64, generator=gen, device=DEV) * 0.01).bfloat16()
+    down = (torch.randn(64, K, generator=gen, device=DEV) * 0.125).bfloat16()
+    w = w0.clone()
+    F.lora_merge_sr_(w, ws, up, down, 0.0, seed=7)
+    assert torch.equal(w, w0)
+    F.lora_merge_sr_(w, ws, up, down, 1.0, seed=7)
+    assert not torch.equal(w, w0)
+    F.lora_merge_sr_(w, ws, up, down, -1.0, seed=7)
+    assert int((w.int() - w0.int()).abs().max()) <= 1
