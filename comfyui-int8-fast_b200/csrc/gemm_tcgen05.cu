@@ -14,6 +14,14 @@
 // The accumulator is double buffered in tensor memory (2 x BN columns) so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
 //
+// PAIR variant (cta_group::2): two CTAs of a cluster work on one 256 x BN
+// tile.  Each loads its own 128 rows of A and its own BN/2 rows of B (half the
+// shared-memory fill bandwidth per SM for the same MMA work), the even CTA
+// issues the 256-row MMAs for both, each keeps and drains its own 128
+// accumulator rows.  Stage-full barriers live in the leader and count both
+// CTAs' TMA bytes; stage-empty / accumulator-full signals are committed to
+// both CTAs; accumulator-empty arrivals of both CTAs go to the leader.
+//
 // Every mbarrier wait is bounded: a wait that runs out writes a code to the
 // device status word, raises a CTA-wide abort flag and all roles fall through
 // to the common teardown (which still frees the tensor memory).
@@ -28,10 +36,9 @@
 namespace i8f {
 namespace {
 
-constexpr int kBM = 128;            // rows of A per tile == TMEM lanes
+constexpr int kBM = 128;            // rows of A per CTA == TMEM lanes
 constexpr int kStageRowBytes = 128; // one 128-byte swizzle span of K per stage
 constexpr int kThreads = 192;
-constexpr int kEpiWarp0 = 2;
 
 enum Kind : int { kKindI8 = 0, kKindBF16 = 1, kKindF16 = 2 };
 enum EpiMode : int { kEpiI32 = 0, kEpiDequant = 1, kEpiCast = 2, kEpiAccum = 3 };
@@ -57,15 +64,18 @@ struct GemmParams {
     int* status;
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 struct Cfg {
+    static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA stages
     static constexpr int kABytes = kBM * kStageRowBytes;
-    static constexpr int kBBytes = BN * kStageRowBytes;
+    static constexpr int kBBytes = kBRows * kStageRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (192 * 1024) / kStageBytes;
     static constexpr int kTmemCols = 2 * BN;  // 512, 256 or 128: powers of two >= 32
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+    static constexpr int kEpiBytes = 4 * 2 * BN * 4;  // per epilogue warp: BN column scales + BN biases (fp32)
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kEpiBytes + 1024;  // + alignment slack
+    static constexpr int kTileM = PAIR ? 2 * kBM : kBM;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
@@ -161,10 +171,13 @@ __device__ __forceinline__ void load_row32(const GemmParams& p, long long row, i
     }
 }
 
-// One 32-column chunk of one accumulator row -> global memory.
+// One 32-column chunk of one accumulator row -> global memory.  `cs` / `cb`
+// point at this chunk's 32 column scales and biases in shared memory (the
+// bias is already rounded to OUT when the reference order asks for it); every
+// lane reads the same address, a broadcast.
 template <int OUT>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, int col, const uint32_t (&v)[32],
-                                               float row_scale, float ws_scalar) {
+                                               float row_scale, float ws_scalar, const float* cs, const float* cb) {
     float y[32];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
@@ -176,30 +189,20 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
             for (int j = 0; j < 32; ++j) y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), total);
         } else if (!single) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float ws = (col + j < p.N) ? __ldg(p.w_scale + col + j) : 0.f;
-                y[j] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[j])), row_scale), ws);
-            }
+            for (int j = 0; j < 32; ++j)
+                y[j] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[j])), row_scale), cs[j]);
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float ws = (col + j < p.N) ? __ldg(p.w_scale + col + j) : 0.f;
-                y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), __fmul_rn(row_scale, ws));
-            }
+            for (int j = 0; j < 32; ++j)
+                y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), __fmul_rn(row_scale, cs[j]));
         }
         if (p.bias != nullptr) {
             if (!single) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float b = (col + j < p.N) ? load_as_f32(p.bias, p.bias_dtype, col + j) : 0.f;
-                    y[j] = __fadd_rn(round_out<OUT>(y[j]), round_out<OUT>(b));
-                }
+                for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), cb[j]);
             } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float b = (col + j < p.N) ? load_as_f32(p.bias, p.bias_dtype, col + j) : 0.f;
-                    y[j] = __fadd_rn(y[j], b);
-                }
+                for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], cb[j]);
             }
         }
     } else if (p.epi_mode == kEpiCast) {
@@ -226,32 +229,33 @@ __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long r
     }
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     constexpr int kElemsPerStage = (KIND == kKindI8) ? kStageRowBytes : kStageRowBytes / 2;
-    constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, kBM, BN)
-                                : (KIND == kKindBF16) ? make_idesc(kDFmtF32, kFmtBF16, kBM, BN)
-                                                      : make_idesc(kDFmtF32, kFmtF16, kBM, BN);
+    constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, C::kTileM, BN)
+                                : (KIND == kKindBF16) ? make_idesc(kDFmtF32, kFmtBF16, C::kTileM, BN)
+                                                      : make_idesc(kDFmtF32, kFmtF16, C::kTileM, BN);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-    const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    constexpr int kBarOff = C::kStages * C::kStageBytes;
     // barrier block: full[kStages], empty[kStages], acc_full[2], acc_empty[2], tmem slot, abort flag
-    const uint32_t full0 = bar_base;
-    const uint32_t empty0 = bar_base + 8 * C::kStages;
-    const uint32_t accfull0 = bar_base + 16 * C::kStages;
+    const uint32_t full0 = smem_base + kBarOff;
+    const uint32_t empty0 = full0 + 8 * C::kStages;
+    const uint32_t accfull0 = full0 + 16 * C::kStages;
     const uint32_t accempty0 = accfull0 + 16;
     const uint32_t tmem_slot = accempty0 + 16;
-    uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot_ptr =
-        reinterpret_cast<volatile uint32_t*>(gen_base + C::kStages * C::kStageBytes + 16 * C::kStages + 32);
-    volatile int* abort_flag =
-        reinterpret_cast<volatile int*>(gen_base + C::kStages * C::kStageBytes + 16 * C::kStages + 36);
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + kBarOff + 16 * C::kStages + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kBarOff + 16 * C::kStages + 36);
+    float* epi_smem = reinterpret_cast<float*>(gen_base + kBarOff + C::kBarrierBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // position in the CTA pair
+    const bool leader = rank == 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -260,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(accfull0 + 8 * b, 1);
-            mbar_init(accempty0 + 8 * b, 4);  // one arrival per epilogue warp
+            mbar_init(accempty0 + 8 * b, PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -269,23 +273,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tma_prefetch_desc(&tmB);
     }
     if (warp == 1) {
-        tmem_alloc<C::kTmemCols>(tmem_slot);
+        if constexpr (PAIR) tmem_alloc_pair<C::kTmemCols>(tmem_slot);
+        else tmem_alloc<C::kTmemCols>(tmem_slot);
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {  // the peer must see initialised barriers before it signals them
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     const int num_tiles = p.tiles_m * p.tiles_n;
+    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int tile_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
 
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            for (int t = tile_first; ok && t < num_tiles; t += tile_step) {
                 int m_blk, n_blk;
                 tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
+                const int row_a = m_blk * C::kTileM + static_cast<int>(rank) * kBM;
+                const int row_b = n_blk * BN + static_cast<int>(rank) * C::kBRows;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.status, kStEmptyWait)) {
                         ok = false;
@@ -293,9 +306,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                     const uint32_t a_dst = smem_base + stage * C::kStageBytes;
                     const uint32_t b_dst = a_dst + C::kABytes;
-                    mbar_arrive_expect_tx(full0 + 8 * stage, C::kStageBytes);
-                    tma_load_2d(a_dst, &tmA, full0 + 8 * stage, kb * kElemsPerStage, m_blk * kBM);
-                    tma_load_2d(b_dst, &tmB, full0 + 8 * stage, kb * kElemsPerStage, n_blk * BN);
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the leader's barrier; the leader alone arms it
+                        const uint32_t bar = mapa_cluster(full0 + 8 * stage, 0);
+                        if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * C::kStageBytes);
+                        tma_load_2d_pair(a_dst, &tmA, bar, kb * kElemsPerStage, row_a);
+                        tma_load_2d_pair(b_dst, &tmB, bar, kb * kElemsPerStage, row_b);
+                    } else {
+                        mbar_arrive_expect_tx(full0 + 8 * stage, C::kStageBytes);
+                        tma_load_2d(a_dst, &tmA, full0 + 8 * stage, kb * kElemsPerStage, row_a);
+                        tma_load_2d(b_dst, &tmB, full0 + 8 * stage, kb * kElemsPerStage, row_b);
+                    }
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -304,13 +325,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             int stage = 0;
             uint32_t phase = 0;
             int buf = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            for (int t = tile_first; ok && t < num_tiles; t += tile_step) {
                 if (!mbar_wait_bounded(accempty0 + 8 * buf, acc_phase ^ 1u, abort_flag, p.status, kStAccEmptyWait)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
@@ -327,35 +348,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int k = 0; k < 4; ++k) {
                         // +32 bytes of K per instruction: 2 in the (address >> 4) field
                         const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                        if constexpr (KIND == kKindI8) mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
-                        else mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                        if constexpr (PAIR) {
+                            if constexpr (KIND == kKindI8) mma_i8_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                            else mma_f16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                        } else {
+                            if constexpr (KIND == kKindI8) mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                            else mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                        }
                     }
-                    mma_commit(empty0 + 8 * stage);  // stage reusable once these MMAs have read it
+                    // stage reusable (in both CTAs) once these MMAs have read it
+                    if constexpr (PAIR) mma_commit_pair(empty0 + 8 * stage);
+                    else mma_commit(empty0 + 8 * stage);
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                mma_commit(accfull0 + 8 * buf);  // accumulator complete
+                if constexpr (PAIR) mma_commit_pair(accfull0 + 8 * buf);  // accumulator complete
+                else mma_commit(accfull0 + 8 * buf);
                 buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }
         }
     } else {
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        float* col_scale = epi_smem + (warp - 2) * 2 * BN;
+        float* col_bias = col_scale + BN;
         int buf = 0;
         uint32_t acc_phase = 0;
-        const float ws_scalar =
-            (p.epi_mode == kEpiDequant && p.w_scale_mode == I8F_WSCALE_TENSOR) ? __ldg(p.w_scale) : 0.f;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const bool dequant = p.epi_mode == kEpiDequant;
+        const bool per_ch = dequant && p.w_scale_mode == I8F_WSCALE_CHANNEL;
+        const bool has_bias = dequant && p.bias != nullptr;
+        const float ws_scalar = (dequant && !per_ch) ? __ldg(p.w_scale) : 0.f;
+        const uint32_t accempty_leader = PAIR ? mapa_cluster(accempty0, 0) : accempty0;
+        for (int t = tile_first; t < num_tiles; t += tile_step) {
             int m_blk, n_blk;
             tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
+            // stage this tile's column scales and biases (fp32) for broadcast reads
+            if (per_ch || has_bias) {
+                __syncwarp();
+                for (int j = lane; j < BN; j += 32) {
+                    const int col = n_blk * BN + j;
+                    const bool in = col < p.N;
+                    if (per_ch) col_scale[j] = in ? __ldg(p.w_scale + col) : 0.f;
+                    if (has_bias) {
+                        float b = in ? load_as_f32(p.bias, p.bias_dtype, col) : 0.f;
+                        if (p.epi_order == I8F_EPI_PYTORCH)
+                            b = p.out_dtype == I8F_BF16 ? round_out<I8F_BF16>(b) : round_out<I8F_F16>(b);
+                        col_bias[j] = b;
+                    }
+                }
+                __syncwarp();
+            }
             if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
             tc_fence_after_sync();
-            const long long row = static_cast<long long>(m_blk) * kBM + quarter * 32 + lane;
+            const long long row = static_cast<long long>(m_blk) * C::kTileM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
-            const float row_scale = (p.epi_mode == kEpiDequant && row_ok) ? __ldg(p.a_scale + row) : 0.f;
+            const float row_scale = (dequant && row_ok) ? __ldg(p.a_scale + row) : 0.f;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -365,13 +415,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const int col = n_blk * BN + c * 32;
                 if (row_ok && col < p.N) {
                     if (p.epi_mode == kEpiI32) store_i32_row32(p, row, col, v);
-                    else if (p.out_dtype == I8F_BF16) epilogue_chunk<I8F_BF16>(p, row, col, v, row_scale, ws_scalar);
-                    else epilogue_chunk<I8F_F16>(p, row, col, v, row_scale, ws_scalar);
+                    else if (p.out_dtype == I8F_BF16)
+                        epilogue_chunk<I8F_BF16>(p, row, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32);
+                    else
+                        epilogue_chunk<I8F_F16>(p, row, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32);
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(accempty0 + 8 * buf);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(accempty_leader + 8 * buf);
+                else mbar_arrive(accempty0 + 8 * buf);
+            }
             buf ^= 1;
             if (buf == 0) acc_phase ^= 1u;
         }
@@ -384,9 +439,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // give copies that are still in flight time to land before the CTA exits
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
+    if constexpr (PAIR) {  // neither CTA may leave while the other can still touch its memory
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after_sync();
-        tmem_dealloc<C::kTmemCols>(tmem_base);
+        if constexpr (PAIR) tmem_dealloc_pair<C::kTmemCols>(tmem_base);
+        else tmem_dealloc<C::kTmemCols>(tmem_base);
     }
 }
 
@@ -427,56 +488,103 @@ int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, 
     return I8F_OK;
 }
 
-int sm_count() {
-    static int cached[64] = {0};
+int current_device() {
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
+    return (dev < 0 || dev >= 64) ? 0 : dev;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    const int dev = current_device();
     if (cached[dev] == 0) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
     return cached[dev] > 0 ? cached[dev] : 148;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool PAIR>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K, GemmParams p,
                 cudaStream_t st) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, PAIR>;
     CUtensorMap tmA, tmB;
     int rc = make_operand_map(&tmA, KIND, a, M, K, lda, kBM);
     if (rc != I8F_OK) return rc;
-    rc = make_operand_map(&tmB, KIND, b, N, K, ldb, BN);
+    rc = make_operand_map(&tmB, KIND, b, N, K, ldb, C::kBRows);
     if (rc != I8F_OK) return rc;
     const int esz = KIND == kKindI8 ? 1 : 2;
     const int k_per_stage = kStageRowBytes / esz;
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
     p.num_k_blocks = static_cast<int>((K + k_per_stage - 1) / k_per_stage);
-    p.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
+    p.tiles_m = static_cast<int>((M + C::kTileM - 1) / C::kTileM);
     p.tiles_n = static_cast<int>((N + BN - 1) / BN);
     p.status = device_status_word();
     I8F_REQUIRE(p.status != nullptr, I8F_ERR_CUDA, "device status word unavailable");
-    auto kern = gemm_tcgen05_kernel<KIND, BN>;
+    auto kern = gemm_tcgen05_kernel<KIND, BN, PAIR>;
     static bool attr_done[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
+    static int max_clusters[64] = {0};
+    const int dev = current_device();
     if (!attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaFuncSetAttribute(smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
+        if (PAIR) {
+            cudaLaunchConfig_t probe{};
+            probe.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
+            probe.blockDim = dim3(kThreads, 1, 1);
+            probe.dynamicSmemBytes = C::kSmemBytes;
+            cudaLaunchAttribute at{};
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = 2;
+            at.val.clusterDim.y = 1;
+            at.val.clusterDim.z = 1;
+            probe.attrs = &at;
+            probe.numAttrs = 1;
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, kern, &probe);
+            if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));
+            max_clusters[dev] = n;
+        }
         attr_done[dev] = true;
     }
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, kThreads, C::kSmemBytes, st>>>(tmA, tmB, p);
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute at{};
+    if (PAIR) {
+        I8F_REQUIRE(max_clusters[dev] > 0, I8F_ERR_CUDA, "no CTA pair fits on this device");
+        const long long clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2;
+        at.val.clusterDim.y = 1;
+        at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+    } else {
+        cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()), 1, 1);
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+    if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "gemm_tcgen05_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tcgen05_kernel");
 }
 
+// Tile shape by problem shape: CTA pairs on 256 x 256 tiles when both extents
+// are large, single CTAs with 128 x {256,128,64} tiles otherwise (LoRA ranks,
+// short batches).
 template <int KIND>
-int launch_gemm_bn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
-                   const GemmParams& p, cudaStream_t st) {
-    // wide tiles for wide outputs; narrow ones when N is small (LoRA rank)
-    if (N > 128) return launch_gemm<KIND, 256>(a, lda, b, ldb, M, N, K, p, st);
-    if (N > 64) return launch_gemm<KIND, 128>(a, lda, b, ldb, M, N, K, p, st);
-    return launch_gemm<KIND, 64>(a, lda, b, ldb, M, N, K, p, st);
+int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
+                     const GemmParams& p, cudaStream_t st) {
+    static const int force_single = [] {
+        const char* e = getenv("I8F_GEMM_SINGLE_CTA");
+        return (e != nullptr && e[0] == '1') ? 1 : 0;
+    }();
+    if (N > 128) {
+        if (M > 128 && !force_single) return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st);
+        return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st);
+    }
+    if (N > 64) return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st);
+    return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st);
 }
 
 int check_operands(const void* a, int64_t lda, const void* b, int64_t ldb, int esz, int64_t M, int64_t N, int64_t K) {
@@ -510,7 +618,7 @@ int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, 
     p.ldo = ldacc;
     p.epi_mode = kEpiI32;
     p.vec_ok = aligned16(acc) && (ldacc % 4 == 0);
-    return launch_gemm_bn<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
 }
 
 int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
@@ -538,7 +646,7 @@ int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const in
     p.epi_mode = kEpiDequant;
     p.epi_order = epilogue_order;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
-    return launch_gemm_bn<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
 }
 
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K) {
@@ -579,8 +687,8 @@ int i8f_lora_down(const void* x, int64_t ldx, const void* lora_a, int64_t lda, v
     p.epi_mode = kEpiCast;
     p.vec_ok = aligned16(t) && (ldt % 8 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == I8F_BF16) return launch_gemm_bn<kKindBF16>(x, ldx, lora_a, lda, M, r, K, p, st);
-    return launch_gemm_bn<kKindF16>(x, ldx, lora_a, lda, M, r, K, p, st);
+    if (dtype == I8F_BF16) return launch_gemm_auto<kKindBF16>(x, ldx, lora_a, lda, M, r, K, p, st);
+    return launch_gemm_auto<kKindF16>(x, ldx, lora_a, lda, M, r, K, p, st);
 }
 
 int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb, void* y, int64_t ldy, int dtype,
@@ -596,8 +704,8 @@ int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb,
     p.epi_mode = kEpiAccum;
     p.vec_ok = aligned16(y) && (ldy % 8 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == I8F_BF16) return launch_gemm_bn<kKindBF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
-    return launch_gemm_bn<kKindF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
+    if (dtype == I8F_BF16) return launch_gemm_auto<kKindBF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
+    return launch_gemm_auto<kKindF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
 }
 
 }  // extern "C"

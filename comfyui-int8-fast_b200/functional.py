@@ -189,6 +189,8 @@ def lora_merge_sr_(w: Tensor, w_scale, up: Tensor, down: Tensor, lora_scale: flo
     if w.dtype != torch.int8 or w.dim() != 2 or w.stride(1) != 1:
         raise ValueError("w must be a 2-D int8 tensor with unit inner stride")
     N, K = w.shape
+    if up.numel() == 0 or down.numel() == 0:   # rank 0: nothing to merge
+        return w
     up = _rows(up.reshape(up.shape[0], -1).to(w.device))
     down = _rows(down.reshape(down.shape[0], -1).to(w.device))
     if up.dtype != down.dtype:
