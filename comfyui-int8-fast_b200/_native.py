@@ -18,6 +18,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libi8f.so"
 I8F_BF16, I8F_F16, I8F_F32 = 0, 1, 2
 WSCALE_TENSOR, WSCALE_CHANNEL = 0, 1
 EPI_PYTORCH, EPI_SINGLE = 0, 1
+STATIC_WORKSPACE_BYTES = 16 * 1024 * 1024 + 256 * 1024
 
 DTYPE_CODE = {torch.bfloat16: I8F_BF16, torch.float16: I8F_F16, torch.float32: I8F_F32}
 
@@ -45,6 +46,8 @@ _PROTOTYPES = {
     "i8f_linear_forward": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                    c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p,
                                    c_size_t, c_void_p]),
+    "i8f_linear_forward_static": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p,
+                                          c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "i8f_lora_down": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                               c_int64, c_void_p]),
     "i8f_lora_up_add": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,

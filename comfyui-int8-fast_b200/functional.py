@@ -155,6 +155,36 @@ def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype
     return out
 
 
+def linear_forward_static(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out: Tensor, hadamard: bool = False,
+                          order: int = nat.EPI_PYTORCH) -> Tensor:
+    """linear_forward into a caller-supplied `out`, using the workspace built into the library.
+
+    For callers that must not allocate device memory: the native call allocates nothing, and this
+    wrapper allocates nothing either as long as `w_scale` is already a device tensor and `bias` is on
+    the device.  Limits and sharing rules are those of i8f_linear_forward_static.
+    """
+    nat.require_device(x.device)
+    if x.dim() != 2 or w.dim() != 2 or x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("x and w must be 2-D with unit inner stride (this wrapper never copies)")
+    M, K = x.shape
+    N = w.shape[0]
+    if out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError(f"out must be [{M},{N}] with unit inner stride")
+    if not isinstance(w_scale, Tensor) or w_scale.device != x.device or w_scale.dtype != torch.float32:
+        raise ValueError("w_scale must be an fp32 tensor on the device (1 element, or N elements)")
+    mode = nat.WSCALE_TENSOR if w_scale.numel() == 1 else nat.WSCALE_CHANNEL
+    if mode == nat.WSCALE_CHANNEL and (w_scale.numel() != N or not w_scale.is_contiguous()):
+        raise ValueError("per-channel w_scale must be contiguous with N elements")
+    if bias is not None and (bias.device != x.device or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous device tensor")
+    nat.check(nat.load().i8f_linear_forward_static(nat.ptr(x), _code(x.dtype), _ld(x), 1 if hadamard else 0, nat.ptr(w),
+                                                   _ld(w), nat.ptr(w_scale), mode, nat.ptr(bias),
+                                                   _code(bias.dtype) if bias is not None else 0, nat.ptr(out),
+                                                   _code(out.dtype), _ld(out), M, N, K, order,
+                                                   nat.current_stream(x.device)), "i8f_linear_forward_static")
+    return out
+
+
 def lora_down(x: Tensor, lora_a: Tensor) -> Tensor:
     """t [M,r] = x [M,K] @ lora_a [r,K]^T, rounded to x's dtype (bf16 or fp16)."""
     nat.require_device(x.device)

@@ -134,6 +134,29 @@ int i8f_linear_forward(const void* x, int x_dtype, int64_t ldx, int hadamard128,
                        int64_t M, int64_t N, int64_t K, int epilogue_order,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* Size of the workspace built into the library for i8f_linear_forward_static. */
+#define I8F_STATIC_WORKSPACE_BYTES (16u * 1024u * 1024u + 256u * 1024u)
+
+/* i8f_linear_forward without a workspace argument, for callers that may not allocate device
+ * memory (a host that owns the whole device through its own pool, a loop that must stay off
+ * the allocator, a sandbox that may only launch on a given stream).  Same arithmetic and
+ * results as i8f_linear_forward; the int8 activations and their scales go to an array that is
+ * part of the library image instead.  The call allocates nothing.
+ *   - Limit: i8f_linear_workspace_bytes(M, K) <= I8F_STATIC_WORKSPACE_BYTES (e.g. M*K up to
+ *     4096 x 4096); larger problems return I8F_ERR_WORKSPACE and launch nothing.
+ *   - The array exists once per GPU that loaded the library and stays until the process exits.
+ *   - All calls share it: calls that may overlap on the GPU (different streams without an
+ *     ordering between them) race.  It keeps the previous call's contents; no part of it
+ *     needs to be zero on entry, every byte a call reads it has written first.
+ *   - The first call on a device resolves the array's device address; make it before any
+ *     stream capture begins.
+ * This entry point has no counterpart in the reference (which always allocates through PyTorch). */
+int i8f_linear_forward_static(const void* x, int x_dtype, int64_t ldx, int hadamard128,
+                              const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                              const void* bias, int bias_dtype,
+                              void* out, int out_dtype, int64_t ldo,
+                              int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
+
 /* Dynamic-LoRA down projection: t [M,r] = round(x [M,K] @ lora_a [r,K]^T) in
  * `dtype` (I8F_BF16 or I8F_F16; x, lora_a and t share it), fp32 accumulation.
  * Replaces F.linear(x_2d, lora_A) at int8_quant.py:768. */
