@@ -20,9 +20,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
-import tempfile
 import time
 from pathlib import Path
 
@@ -46,55 +44,66 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and clock-event reasons of one GPU through NVML (read-only queries) from a
+    thread while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake"}
 
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.file = None
+    def __init__(self, torch_device_index: int, period_s: float = 0.004):
+        self.idx = torch_device_index
+        self.period = period_s
+        self.samples = []
+        self.thread = None
+        self.stop_flag = False
+        self.handle = None
+        self.nv = None
 
     def start(self):
         try:
-            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
-                                         stdout=self.file, stderr=subprocess.DEVNULL)
+            import threading
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.idx).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:  # noqa: BLE001
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.idx)
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
         except Exception:  # noqa: BLE001
-            self.proc = None
+            self.thread = None
+
+    def _run(self):
+        nv, h = self.nv, self.handle
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag:
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1e3,
+                                     int(reasons_fn(h))))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
+        if self.thread is None:
             return out
-        self.proc.terminate()
+        self.stop_flag = True
+        self.thread.join(timeout=2)
         try:
-            self.proc.wait(timeout=5)
+            out["sm_max_mhz"] = float(self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
         except Exception:  # noqa: BLE001
-            self.proc.kill()
-        self.file.flush()
-        rows = [r.strip().split(",") for r in Path(self.file.name).read_text().splitlines() if r.strip()]
-        os.unlink(self.file.name)
-        sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in rows:
-            if len(r) < 7:
-                continue
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-                power.append(float(r[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, r[3:7]):
-                if v.strip().lower().startswith("active"):
-                    reasons.add(name)
-        if sm:
-            sm.sort()
-            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), power_w_max=max(power), reasons=sorted(reasons),
-                       samples=len(sm))
+            pass
+        if self.samples:
+            sm = sorted(s[0] for s in self.samples)
+            mask = 0
+            for s_ in self.samples:
+                mask |= s_[2]
+            out.update(sm_mhz=float(sm[len(sm) // 2]), sm_min_mhz=float(sm[0]), power_w_max=max(s[1] for s in self.samples),
+                       reasons=sorted(name for bit, name in self.REASONS.items() if mask & bit), samples=len(self.samples))
         return out
 
 
@@ -325,8 +334,8 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", choices=["c0", "c1", "c2"], default="c1")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     args = ap.parse_args()

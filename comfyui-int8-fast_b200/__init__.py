@@ -11,7 +11,7 @@ import logging
 
 import torch
 
-from . import _native, functional, quarot, workloads  # noqa: F401
+from . import _native, functional, parallel, quarot, workloads  # noqa: F401
 
 
 def _register_layouts():

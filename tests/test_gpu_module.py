@@ -1,0 +1,201 @@
+"""The module layer (Int8TensorwiseOps.Linear, the LoRA adapters, the public functions) on a B200,
+against the oracle and the fixtures recorded from the reference's own module."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bitspec as bs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+
+
+def rms(a):
+    return float(np.sqrt(np.mean(np.asarray(a, dtype=np.float64) ** 2)))
+
+
+def to_np(t):
+    return t.detach().float().cpu().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
+
+
+def bf16(bits):
+    return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)
+
+
+@pytest.fixture()
+def ops(cuda_pkg):
+    o = cuda_pkg.Int8TensorwiseOps
+    saved = (o.excluded_names, o.dynamic_quantize, o.enable_quarot, o._is_prequantized)
+    import comfy.model_management as mm
+    mm._FORCED_DEVICE = torch.device(DEV)
+    yield o
+    o.excluded_names, o.dynamic_quantize, o.enable_quarot, o._is_prequantized = saved
+    mm._FORCED_DEVICE = None
+
+
+def make_linear(ops, sd, K, N, bias=True):
+    lin = ops.Linear(K, N, bias=bias)
+    lin._load_from_state_dict(dict(sd), "", {}, True, [], [], [])
+    return lin.to(DEV)
+
+
+def test_module_forward_matches_reference_fixture(cuda_pkg, ops, golden):
+    g = golden("module_small.npz")
+    M, K = g["x_bits"].shape
+    N = g["wq"].shape[0]
+    lin = make_linear(ops, {"weight": torch.from_numpy(g["wq"]), "weight_scale": torch.from_numpy(g["ws"]),
+                            "bias": bf16(g["bias_bits"])}, K, N)
+    x3 = bf16(g["x_bits"]).reshape(4, 12, K).to(DEV)
+    y = lin(x3)
+    assert y.shape == (4, 12, N) and y.dtype == torch.bfloat16
+    assert np.array_equal(y.reshape(M, N).cpu().view(torch.int16).numpy().view(np.uint16), g["y_bits"])
+    # small-batch branch (M <= 16): dequantised weights, plain matmul
+    y_small = lin(x3[:1, :8])
+    want = bs.bf16_bits_to_f32(g["y_small_bits"])
+    assert np.max(np.abs(to_np(y_small.reshape(8, N)) - want)) <= TOL * rms(want)
+    # dynamic LoRA set on the module, as the hook does
+    lin.lora_A, lin.lora_B = bf16(g["lora_a_bits"]).to(DEV), bf16(g["lora_b_bits"]).to(DEV)
+    y_lora = lin(x3)
+    want = bs.bf16_bits_to_f32(g["y_lora_bits"])
+    assert np.max(np.abs(to_np(y_lora.reshape(M, N)) - want)) <= TOL * rms(want)
+    lin.lora_A = lin.lora_B = None
+    assert torch.equal(lin(x3), y)
+
+
+def test_module_cast_path_and_fp32_input(cuda_pkg, ops):
+    """comfy_cast_weights (offloaded weights) goes through cast_bias_weight / uncast_bias_weight; an fp32
+    activation is computed in bf16 as the reference does."""
+    wl, F = cuda_pkg.workloads, cuda_pkg.functional
+    K, N = 256, 136
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(N, K, seed=2).numpy())
+    lin = ops.Linear(K, N, bias=True)
+    lin._load_from_state_dict({"weight": torch.from_numpy(wq), "weight_scale": torch.from_numpy(ws),
+                               "bias": wl.bias_fp32(N, seed=2)}, "", {}, True, [], [], [])
+    lin.comfy_cast_weights = True                      # weights stay on the CPU, cast per call
+    x = wl.activation(40, K, seed=2).to(DEV)
+    y = lin(x)
+    assert lin._cast_calls == 1 and lin._uncast_calls == 1 and y.device.type == "cuda"
+    want = bs.linear_w8a8(to_np(x), wq, ws, wl.bias_fp32(N, seed=2).numpy())
+    assert np.array_equal(to_np(y), want)
+    y32 = lin(x.float())
+    assert y32.dtype == torch.bfloat16 and torch.equal(y32, y)
+
+
+def test_on_the_fly_quantisation_with_quarot(cuda_pkg, ops):
+    wl = cuda_pkg.workloads
+    K, N = 512, 200
+    w = wl.weight_fp32(N, K, seed=4)
+    ops.dynamic_quantize, ops.enable_quarot = True, True
+    lin = make_linear(ops, {"weight": w.bfloat16(), "bias": wl.bias_fp32(N, seed=4).bfloat16()}, K, N)
+    assert lin._is_quantized and lin._is_per_row and lin._use_quarot and lin.weight.dtype == torch.int8
+    wq, ws = bs.quantize_rowwise(bs.rotate_weight(to_np(w.bfloat16())))
+    assert np.array_equal(to_np(lin.weight), wq) and np.array_equal(to_np(lin.weight_scale), ws)
+    x = wl.activation(64, K, seed=4).to(DEV)
+    want = bs.linear_w8a8(to_np(x), wq, ws, to_np(wl.bias_fp32(N, seed=4).bfloat16()), hadamard=True)
+    assert np.array_equal(to_np(lin(x)), want)
+    # the rotation preserves the product: compare with the unquantised linear
+    ref = to_np(x) @ to_np(w.bfloat16()).T + to_np(wl.bias_fp32(N, seed=4).bfloat16())
+    assert np.max(np.abs(to_np(lin(x)) - ref)) <= 0.05 * rms(ref)
+    # dynamic LoRA with QuaRot: the reference feeds the rotated activations (default), the flag turns that off
+    a, b = wl.lora_factors(N, K, 16, seed=4)
+    lin.lora_A, lin.lora_B = a.to(DEV), b.to(DEV)
+    xr = bs.rotate_activation(to_np(x))
+    want_rot = bs.lora_up_add(want, bs.lora_down(xr, to_np(a)), to_np(b))
+    assert np.max(np.abs(to_np(lin(x)) - want_rot)) <= TOL * rms(want_rot)
+    ops.lora_uses_rotated_input = False
+    try:
+        want_plain = bs.lora_up_add(want, bs.lora_down(to_np(x), to_np(a)), to_np(b))
+        assert np.max(np.abs(to_np(lin(x)) - want_plain)) <= TOL * rms(want_plain)
+    finally:
+        ops.lora_uses_rotated_input = True
+    # K not a multiple of 128: rotation is skipped, quantisation still happens
+    lin2 = make_linear(ops, {"weight": wl.weight_fp32(48, 80, seed=5)}, 80, 48, bias=False)
+    assert lin2._is_quantized and not lin2._use_quarot
+
+
+def test_public_functions(cuda_pkg):
+    o, wl = cuda_pkg.ops, cuda_pkg.workloads
+    x = wl.activation(50, 256, seed=6).to(DEV)
+    q, s = o.quantize_int8_axiswise(x.reshape(5, 10, 256), dim=-1)
+    q_want, s_want = bs.quantize_rowwise(to_np(x))
+    assert q.shape == (5, 10, 256) and s.shape == (5, 10, 1)
+    assert np.array_equal(to_np(q).reshape(50, 256), q_want) and np.array_equal(to_np(s).reshape(50, 1), s_want)
+    w = wl.weight_fp32(72, 256, seed=6).to(DEV)
+    wq, ws = o.quantize_int8_tensorwise(w)
+    wq_want, ws_want = bs.quantize_tensorwise(to_np(w))
+    assert np.array_equal(to_np(wq), wq_want) and float(ws) == float(ws_want) and ws.dim() == 0
+    assert np.array_equal(to_np(o.quantize_int8(w, ws)), wq_want)
+    assert torch.equal(o.dequantize(wq, ws), wq.float() * ws)
+    y = o.int8_forward_dynamic(x, wq, float(ws), None, torch.bfloat16)
+    assert np.array_equal(to_np(y), bs.linear_w8a8(to_np(x), wq_want, ws_want, None))
+    wq2, ws2 = o.quantize_int8_axiswise(w, dim=1)
+    y2 = o.int8_forward_dynamic_per_row(x, wq2, ws2, None, torch.bfloat16)
+    assert np.array_equal(to_np(y2), bs.linear_w8a8(to_np(x), *bs.quantize_rowwise(to_np(w)), None))
+    d = torch.randn(72, 256, generator=torch.Generator().manual_seed(1)) * 0.01
+    sr = o.stochastic_round_int8_delta(d, ws2.cpu(), seed=99)          # CPU in, CPU out, computed on the GPU
+    assert sr.device.type == "cpu"
+    assert np.array_equal(sr.numpy(), bs.stochastic_round(d.numpy(), to_np(ws2), bs.philox_uniforms(99, 72, 256)))
+    hr = cuda_pkg.quarot.rotate_activation(x, None, 128)
+    assert np.array_equal(to_np(hr), bs.rotate_activation(to_np(x)))
+    wr = cuda_pkg.quarot.rotate_weight(w, None, 128)
+    assert np.array_equal(to_np(wr), bs.rotate_weight(to_np(w)))
+
+
+def test_patch_adapters_merge_in_int8_space(cuda_pkg, ops):
+    """INT8LoRAPatchAdapter / INT8MergedLoRAPatchAdapter against the oracle (Philox uniforms keyed by the seed)."""
+    o, wl = cuda_pkg.ops, cuda_pkg.workloads
+    N, K, r = 192, 256, 8
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(N, K, seed=7).numpy())
+    down, up = wl.lora_factors(N, K, r, seed=7)
+    up = (up.float() * 40).bfloat16()
+    u = bs.philox_uniforms(318008, N, K)
+    weight = torch.from_numpy(wq)                                     # ComfyUI hands over the CPU weight
+    ad = o.INT8LoRAPatchAdapter({"k"}, (up, down, 4.0, None, None, None), torch.from_numpy(ws), seed=318008)
+    out = ad.calculate_weight(weight, "k", 0.5, 1.0, None, None, intermediate_dtype=torch.int8)
+    assert out.device.type == "cpu" and out.dtype == torch.int8 and out is not weight
+    want = bs.lora_merge(wq, ws, to_np(up), to_np(down), 4.0 / r * 0.5, u)
+    assert np.array_equal(out.numpy(), want) and np.array_equal(weight.numpy(), wq)
+    # fused-QKV slice: rows [64, 128) of the scale vector
+    ad_up = o.INT8LoRAPatchAdapter({"k"}, (up[64:128], down, 4.0, None, None, None), torch.from_numpy(ws), seed=318008)
+    sl2 = ad_up.calculate_weight(weight[64:128].clone(), "k", 0.5, 1.0, (0, 64, 64), None)
+    want_sl = bs.lora_merge(wq[64:128], ws[64:128], to_np(up[64:128]), to_np(down), 4.0 / r * 0.5, u[:64])
+    assert np.array_equal(sl2.numpy(), want_sl) and sl2.shape == (64, K)
+    # QuaRot on: the delta is rotated like the weights were
+    ops.enable_quarot = True
+    rot = ad.calculate_weight(weight.to(DEV), "k", 0.5, 1.0, None, None)
+    assert rot.device.type == "cuda"
+    assert np.array_equal(to_np(rot), bs.lora_merge(wq, ws, to_np(up), to_np(down), 4.0 / r * 0.5, u, hadamard=True))
+    ops.enable_quarot = False
+    # Tucker-mid LoRA takes the reconstruct path (delta built with torch, rounded by the kernel)
+    mid = torch.randn(r, r, generator=torch.Generator().manual_seed(3))
+    ad_mid = o.INT8LoRAPatchAdapter({"k"}, (up.float(), down.float(), None, mid, None, None), torch.from_numpy(ws), seed=5)
+    out_mid = ad_mid.calculate_weight(weight, "k", 1.0, 1.0, None, None)
+    delta = (up.float() @ (mid @ down.float())).numpy()
+    want_mid = np.clip(wq.astype(np.int32) + bs.stochastic_round(delta, ws, bs.philox_uniforms(5, N, K)), -128, 127)
+    assert (out_mid.numpy() != want_mid).mean() <= 1e-3          # torch.mm order vs NumPy order in the delta
+    # float weights: ordinary additive patch
+    wf = wl.weight_fp32(N, K, seed=7)
+    outf = ad.calculate_weight(wf, "k", 0.5, 1.0, None, None)
+    assert torch.allclose(outf, wf + (up.float() @ down.float()) * (4.0 / r * 0.5), atol=1e-5)
+    # stack: two LoRAs, one rounding
+    down2, up2 = wl.lora_factors(N, K, 4, seed=8)
+    base = type("A", (), {})
+    a1, a2 = base(), base()
+    a1.loaded_keys, a1.weights = {"k"}, (up, down, 4.0, None, None, None)
+    a2.loaded_keys, a2.weights = {"k"}, (up2, down2, None, None, None, None)
+    merged = o.INT8MergedLoRAPatchAdapter([(a1, 0.5), (a2, -2.0)], torch.from_numpy(ws), seed=318008)
+    got = merged.calculate_weight(weight, "k", 1.0, 1.0, None, None)
+    cat_up = np.concatenate([to_np(up) * np.float32(4.0 / r * 0.5), to_np(up2) * np.float32(-2.0)], axis=1)
+    cat_down = np.concatenate([to_np(down), to_np(down2)], axis=0)
+    assert np.array_equal(got.numpy(), bs.lora_merge(wq, ws, cat_up, cat_down, 1.0, u))
+
+
+def test_set_weight_requantises_float_results(cuda_pkg, ops):
+    wl = cuda_pkg.workloads
+    N, K = 64, 128
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(N, K, seed=9).numpy())
+    lin = make_linear(ops, {"weight": torch.from_numpy(wq), "weight_scale": torch.from_numpy(ws)}, K, N, bias=False)
+    newf = wl.weight_fp32(N, K, seed=10)
+    got = lin.set_weight(newf, seed=77, return_weight=True)
+    assert np.array_equal(to_np(got), bs.stochastic_round(newf.numpy(), ws, bs.philox_uniforms(77, N, K)))
