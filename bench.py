@@ -82,17 +82,19 @@ class ClockSampler:
         while not self.stop_flag:
             try:
                 self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetPowerUsage(h) / 1e3,
-                                     int(reasons_fn(h))))
+                                     int(reasons_fn(h)), time.perf_counter()))
             except Exception:  # noqa: BLE001
                 pass
             time.sleep(self.period)
 
-    def stop(self):
+    def stop(self, t_begin: float = 0.0, t_end: float = float("inf")):
+        """Summary of the samples taken between the two host timestamps (the timed region)."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.thread is None:
             return out
         self.stop_flag = True
         self.thread.join(timeout=2)
+        self.samples = [s for s in self.samples if t_begin <= s[3] <= t_end]
         try:
             out["sm_max_mhz"] = float(self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
         except Exception:  # noqa: BLE001
@@ -261,13 +263,15 @@ def run_gpu_arm(args):
         time.sleep(0.15)
     sync_all()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    host_t0 = time.perf_counter()
     t_start.record()
     for i in range(args.steps):
         step(i, True)
     t_end.record()
     sync_all()
+    host_t1 = time.perf_counter()
     elapsed_ms = t_start.elapsed_time(t_end)
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(host_t0, host_t1) if sampler else None
     gemm_ms = sorted(a.elapsed_time(b) for a, b in gemm_events)
     gemm_avg_ms = sum(gemm_ms) / len(gemm_ms)
 
@@ -324,24 +328,186 @@ def run_gpu_arm(args):
         "cpu_baseline": cpu_base,
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                 "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * args.steps * world,
         "clocks": clocks,
         "device_status": status,
     }
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------- DiT workload
+def dit_config_dict(cfg, world, graph):
+    return {"workload": "c3_synthetic_dit_step", "batch_per_gpu": 1, "img_tokens": cfg.img_tokens,
+            "txt_tokens": cfg.txt_tokens, "hidden": cfg.hidden, "heads": cfg.heads, "double_blocks": cfg.double_blocks,
+            "single_blocks": cfg.single_blocks, "int8_params_B": cfg.int8_params() / 1e9,
+            "int8_TOP_per_step": cfg.int8_ops() / 1e12, "attention_TFLOP_per_step": cfg.attention_flops() / 1e12,
+            "linears": "int8 tensorwise weights, per-token activation quant", "attention": "bf16 SDPA",
+            "parallelism": f"one sample per GPU x{world}", "cuda_graph": graph,
+            "l2": "6.7 GB of int8 weights stream through the 126 MB L2 every step"}
+
+
+def dit_cpu_seconds(cfg, budget_s: float):
+    """CPU estimate of one step: the oracle linear timed on 512 tokens of the two MLP shapes, scaled by op count
+    (attention and element-wise work are left out, which favours the CPU)."""
+    import __graft_entry__ as g
+    wl = g.load_package().workloads
+    rates = []
+    for name in ("c1_quarot_mlp_up",):
+        base, _ = cpu_reference_rate(wl.LinearShape(name, 4608, cfg.hidden, cfg.mlp_hidden, False, False, True), 10, 2, budget_s)
+        rates.append(base)
+    tops = sum(r["value"] for r in rates) / len(rates)
+    return cfg.int8_ops() / (tops * 1e12), rates[0]
+
+
+def run_dit(args):
+    import importlib
+    import torch
+    import __graft_entry__ as g
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    pkg = g.load_package()
+    dit = importlib.import_module(pkg.__name__ + ".dit")
+    cfg = dit.DiTConfig()
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        sec, base = dit_cpu_seconds(cfg, budget_s=40.0)
+        base = dict(base, value=sec, unit="s/it", sample=base["sample"] + "; step time = int8 ops / that rate")
+        print(json.dumps({"impl": "reference", "metric": "dit_step_time", "value": sec, "unit": "s/it", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                          "config": dit_config_dict(cfg, max(1, args.gpus), False), "cpu_baseline": base,
+                          "e2e": {"value": sec, "unit": "s/it", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    model = dit.SyntheticDiT(cfg, seed=0, device=dev)
+    gen = torch.Generator().manual_seed(1000 + rank)
+    img_h = torch.randn(1, cfg.img_tokens, cfg.in_channels, generator=gen).bfloat16().pin_memory()
+    txt_h = torch.randn(1, cfg.txt_tokens, cfg.txt_dim, generator=gen).bfloat16().pin_memory()
+    out_h = torch.empty(1, cfg.img_tokens, cfg.in_channels, dtype=torch.bfloat16).pin_memory()
+    img, txt = img_h.to(dev), txt_h.to(dev)
+    t = torch.full((1,), 0.5, device=dev)
+    steps = min(args.steps, 20)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(3, min(args.warmup, 5))):
+        out = model(img, txt, t)
+    sync_all()
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                model(img, txt, t)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = model(img, txt, t)
+            graph.replay()
+            sync_all()
+        except Exception as e:  # noqa: BLE001
+            print(f"CUDA graph capture failed ({e!r}); running eagerly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def step():
+        nonlocal out
+        if graph is not None:
+            graph.replay()
+        else:
+            out = model(img, txt, t)
+
+    for _ in range(3):
+        step()
+    sync_all()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    host_t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sync_all()
+    host_t1 = time.perf_counter()
+    ms = e0.elapsed_time(e1) / steps
+    clocks = sampler.stop(host_t0, host_t1) if sampler else None
+
+    def e2e_step():
+        img.copy_(img_h, non_blocking=True)
+        txt.copy_(txt_h, non_blocking=True)
+        step()
+        out_h.copy_(out, non_blocking=True)
+
+    e2e_step()
+    sync_all()
+    e0.record()
+    for _ in range(steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1) / steps
+    status = pkg._native.device_status()
+    finite = bool(torch.isfinite(out.float()).all())
+    if dist is not None:
+        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in tt.tolist())
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    n_int8 = cfg.double_blocks * 8 + cfg.single_blocks * 2
+    peaks, peak_kind = measured_peaks()
+    peak_tops = 2.0 * peaks["bf16_tflops_sustained"]
+    achieved = cfg.int8_ops() / (ms * 1e-3) / 1e12
+    cpu_sec, cpu_base = dit_cpu_seconds(cfg, budget_s=12.0)
+    cpu_base = dict(cpu_base, value=cpu_sec, unit="s/it", sample=cpu_base["sample"] + "; step time = int8 ops / that rate")
+    print(json.dumps({
+        "metric": "dit_step_time", "value": ms * 1e-3, "unit": "s/it", "n_gpus": world, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic", "config": dit_config_dict(cfg, world, graph is not None),
+        "samples_per_s_all_gpus": world / (ms * 1e-3),
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8,256> (whole step)", "achieved": achieved,
+                     "peak": peak_tops, "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": None,
+                     "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} MEASURED_PEAKS.json; achieved = int8 linear ops "
+                                    "/ WHOLE step time (attention, norms and element-wise work included in the time)",
+                     "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
+        "cpu_baseline": cpu_base,
+        "e2e": {"value": e2e_ms * 1e-3, "unit": "s/it", "h2d_bytes_per_step": img_h.numel() * 2 + txt_h.numel() * 2,
+                "d2h_bytes_per_step": out_h.numel() * 2, "steps": steps},
+        "gpu_launches": 2 * n_int8 * steps * world, "clocks": clocks, "device_status": status, "output_finite": finite}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "dit"], default="c1")
+    ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.workload == "dit":
+        run_dit(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -1,0 +1,185 @@
+"""Synthetic rectified-flow DiT denoising step (benchmark workload, random weights).
+
+Stands in for the 9B-class Flux-style model the node pack's README timed (no checkpoint is
+available offline): hidden 4096, 32 heads x 128, MLP ratio 3 with GELU, 8 double-stream and 24
+single-stream blocks, 4096 image tokens (1024 x 1024 px) plus 512 text tokens.  Every q/k/v/o/MLP
+linear is an int8 tensorwise-weight layer with dynamic per-token activation quantisation (the W8A8
+hot path); input/output embedders, time embedding and the modulation linears stay bf16, mirroring
+the layers the loader excludes for flux2.  Attention runs in bf16 through
+torch.nn.functional.scaled_dot_product_attention.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as TF
+from torch import Tensor, nn
+
+from .ops import StandaloneInt8Ops as Ops
+
+
+@dataclass(frozen=True)
+class DiTConfig:
+    hidden: int = 4096
+    heads: int = 32
+    mlp_ratio: int = 3
+    double_blocks: int = 8
+    single_blocks: int = 24
+    img_tokens: int = 4096
+    txt_tokens: int = 512
+    in_channels: int = 64
+    txt_dim: int = 4096
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+    @property
+    def mlp_hidden(self) -> int:
+        return self.hidden * self.mlp_ratio
+
+    def int8_params(self) -> int:
+        h, m = self.hidden, self.mlp_hidden
+        per_stream = 3 * h * h + h * h + 2 * h * m
+        return self.double_blocks * 2 * per_stream + self.single_blocks * ((3 * h + m) * h + (h + m) * h)
+
+    def int8_ops(self, batch: int = 1) -> float:
+        """2*M*N*K summed over the int8 linears of one step."""
+        h, m = self.hidden, self.mlp_hidden
+        per_stream = 3 * h * h + h * h + 2 * h * m
+        tok = self.img_tokens + self.txt_tokens
+        return 2.0 * batch * (self.double_blocks * per_stream * tok + self.single_blocks * ((3 * h + m) * h + (h + m) * h) * tok)
+
+    def attention_flops(self, batch: int = 1) -> float:
+        tok = self.img_tokens + self.txt_tokens
+        return 4.0 * batch * (self.double_blocks + self.single_blocks) * tok * tok * self.hidden
+
+
+def int8_linear(in_f: int, out_f: int, gen: torch.Generator, device, bias: bool = True) -> nn.Module:
+    """An Int8 ops Linear with random N(0, 0.02) weights quantised tensorwise on the device."""
+    from . import functional as F
+    lin = Ops.Linear(in_f, out_f, bias=bias, device="meta")
+    w = (torch.randn(out_f, in_f, generator=gen, device=device, dtype=torch.float32) * 0.02)
+    q, scale = F.quantize_tensorwise(w)
+    sd = {"weight": q, "weight_scale": scale.reshape(1).clone()}
+    if bias:
+        sd["bias"] = torch.zeros(out_f, device=device, dtype=torch.bfloat16)
+    lin._load_from_state_dict(sd, "", {}, True, [], [], [])
+    return lin
+
+
+def bf16_linear(in_f: int, out_f: int, gen: torch.Generator, device) -> nn.Linear:
+    lin = nn.Linear(in_f, out_f, bias=True, device=device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(out_f, in_f, generator=gen, device=device) * 0.02)
+        lin.bias.zero_()
+    return lin
+
+
+def rms_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    return (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def modulate(x: Tensor, shift: Tensor, scale: Tensor) -> Tensor:
+    return TF.layer_norm(x, x.shape[-1:]) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, heads: int) -> Tensor:
+    b, t, h = q.shape
+    q, k, v = (z.view(b, t, heads, h // heads).transpose(1, 2) for z in (q, k, v))
+    return TF.scaled_dot_product_attention(rms_norm(q), rms_norm(k), v).transpose(1, 2).reshape(b, t, h)
+
+
+class StreamBlock(nn.Module):
+    """One stream (image or text) of a double block."""
+
+    def __init__(self, cfg: DiTConfig, gen, device):
+        super().__init__()
+        h, m = cfg.hidden, cfg.mlp_hidden
+        self.mod = bf16_linear(h, 6 * h, gen, device)
+        self.qkv = int8_linear(h, 3 * h, gen, device)
+        self.proj = int8_linear(h, h, gen, device)
+        self.mlp_up = int8_linear(h, m, gen, device)
+        self.mlp_down = int8_linear(m, h, gen, device)
+
+
+class DoubleBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, gen, device):
+        super().__init__()
+        self.cfg = cfg
+        self.img = StreamBlock(cfg, gen, device)
+        self.txt = StreamBlock(cfg, gen, device)
+
+    def forward(self, img: Tensor, txt: Tensor, vec: Tensor):
+        cfg = self.cfg
+        mods = {}
+        qkv = {}
+        for name, x, blk in (("txt", txt, self.txt), ("img", img, self.img)):
+            mods[name] = blk.mod(TF.silu(vec)).chunk(6, dim=-1)
+            qkv[name] = blk.qkv(modulate(x, mods[name][0], mods[name][1])).chunk(3, dim=-1)
+        q, k, v = (torch.cat([qkv["txt"][i], qkv["img"][i]], dim=1) for i in range(3))
+        attn = attention(q, k, v, cfg.heads)
+        outs = []
+        for name, x, blk, a in (("txt", txt, self.txt, attn[:, : txt.shape[1]]), ("img", img, self.img, attn[:, txt.shape[1]:])):
+            sh1, sc1, g1, sh2, sc2, g2 = mods[name]
+            x = x + g1.unsqueeze(1) * blk.proj(a)
+            x = x + g2.unsqueeze(1) * blk.mlp_down(TF.gelu(blk.mlp_up(modulate(x, sh2, sc2)), approximate="tanh"))
+            outs.append(x)
+        return outs[1], outs[0]
+
+
+class SingleBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, gen, device):
+        super().__init__()
+        self.cfg = cfg
+        h, m = cfg.hidden, cfg.mlp_hidden
+        self.mod = bf16_linear(h, 3 * h, gen, device)
+        self.linear1 = int8_linear(h, 3 * h + m, gen, device)
+        self.linear2 = int8_linear(h + m, h, gen, device)
+
+    def forward(self, x: Tensor, vec: Tensor) -> Tensor:
+        h = self.cfg.hidden
+        shift, scale, gate = self.mod(TF.silu(vec)).chunk(3, dim=-1)
+        y = self.linear1(modulate(x, shift, scale))
+        q, k, v, mlp = y[..., :h], y[..., h:2 * h], y[..., 2 * h:3 * h], y[..., 3 * h:]
+        a = attention(q, k, v, self.cfg.heads)
+        return x + gate.unsqueeze(1) * self.linear2(torch.cat([a, TF.gelu(mlp, approximate="tanh")], dim=-1))
+
+
+def timestep_embedding(t: Tensor, dim: int = 256) -> Tensor:
+    half = dim // 2
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
+    args = t.float()[:, None] * 1000.0 * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class SyntheticDiT(nn.Module):
+    def __init__(self, cfg: DiTConfig = DiTConfig(), seed: int = 0, device="cuda"):
+        super().__init__()
+        self.cfg = cfg
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)
+        h = cfg.hidden
+        self.img_in = bf16_linear(cfg.in_channels, h, gen, device)
+        self.txt_in = bf16_linear(cfg.txt_dim, h, gen, device)
+        self.time_in = nn.Sequential(bf16_linear(256, h, gen, device), nn.SiLU(), bf16_linear(h, h, gen, device))
+        self.double = nn.ModuleList([DoubleBlock(cfg, gen, device) for _ in range(cfg.double_blocks)])
+        self.single = nn.ModuleList([SingleBlock(cfg, gen, device) for _ in range(cfg.single_blocks)])
+        self.final_mod = bf16_linear(h, 2 * h, gen, device)
+        self.final = bf16_linear(h, cfg.in_channels, gen, device)
+
+    @torch.no_grad()
+    def forward(self, img: Tensor, txt: Tensor, t: Tensor) -> Tensor:
+        """img [B, img_tokens, in_channels], txt [B, txt_tokens, txt_dim], t [B] in [0,1] -> velocity [B, img_tokens, in_channels]."""
+        vec = self.time_in(timestep_embedding(t).to(torch.bfloat16))
+        img, txt = self.img_in(img), self.txt_in(txt)
+        for blk in self.double:
+            img, txt = blk(img, txt, vec)
+        x = torch.cat([txt, img], dim=1)
+        for blk in self.single:
+            x = blk(x, vec)
+        x = x[:, txt.shape[1]:]
+        shift, scale = self.final_mod(TF.silu(vec)).chunk(2, dim=-1)
+        return self.final(modulate(x, shift, scale))

@@ -594,3 +594,34 @@ except ImportError:
     _COMFY_OPS_AVAILABLE = False
 
 Int8TensorwiseOps = _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight) if _COMFY_OPS_AVAILABLE else None
+
+
+# -----------------------------------------------------------------------------
+# The same ops class without ComfyUI (benchmarks, stand-alone use): plain torch layers as the base and
+# no weight-offloading handshake (weights live on the device).
+# -----------------------------------------------------------------------------
+class _PlainBase:
+    class Linear(nn.Linear):
+        comfy_cast_weights = False
+
+        def __init__(self, in_features, out_features, bias=True, device=None, dtype=None):
+            super().__init__(in_features, out_features, bias=bias, device=device, dtype=dtype)
+            self.weight_function = []
+            self.bias_function = []
+
+    GroupNorm, LayerNorm, Conv2d, Conv3d = nn.GroupNorm, nn.LayerNorm, nn.Conv2d, nn.Conv3d
+    ConvTranspose2d, Embedding = nn.ConvTranspose2d, nn.Embedding
+
+
+def _plain_cast(module, input=None, dtype=None, device=None, bias_dtype=None, offloadable=False):
+    if input is not None:
+        dtype, device = input.dtype, input.device
+    bias = None if module.bias is None else module.bias.to(device=device, dtype=bias_dtype or dtype)
+    return module.weight.to(device=device, dtype=dtype), bias, None
+
+
+def _plain_uncast(module, weight, bias, offload_stream):
+    return None
+
+
+StandaloneInt8Ops = _define_ops(_PlainBase, _plain_cast, _plain_uncast)
