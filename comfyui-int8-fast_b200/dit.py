@@ -165,8 +165,8 @@ class SyntheticDiT(nn.Module):
         self.img_in = bf16_linear(cfg.in_channels, h, gen, device)
         self.txt_in = bf16_linear(cfg.txt_dim, h, gen, device)
         self.time_in = nn.Sequential(bf16_linear(256, h, gen, device), nn.SiLU(), bf16_linear(h, h, gen, device))
-        self.double = nn.ModuleList([DoubleBlock(cfg, gen, device) for _ in range(cfg.double_blocks)])
-        self.single = nn.ModuleList([SingleBlock(cfg, gen, device) for _ in range(cfg.single_blocks)])
+        self.double_stream = nn.ModuleList([DoubleBlock(cfg, gen, device) for _ in range(cfg.double_blocks)])
+        self.single_stream = nn.ModuleList([SingleBlock(cfg, gen, device) for _ in range(cfg.single_blocks)])
         self.final_mod = bf16_linear(h, 2 * h, gen, device)
         self.final = bf16_linear(h, cfg.in_channels, gen, device)
 
@@ -175,10 +175,10 @@ class SyntheticDiT(nn.Module):
         """img [B, img_tokens, in_channels], txt [B, txt_tokens, txt_dim], t [B] in [0,1] -> velocity [B, img_tokens, in_channels]."""
         vec = self.time_in(timestep_embedding(t).to(torch.bfloat16))
         img, txt = self.img_in(img), self.txt_in(txt)
-        for blk in self.double:
+        for blk in self.double_stream:
             img, txt = blk(img, txt, vec)
         x = torch.cat([txt, img], dim=1)
-        for blk in self.single:
+        for blk in self.single_stream:
             x = blk(x, vec)
         x = x[:, txt.shape[1]:]
         shift, scale = self.final_mod(TF.silu(vec)).chunk(2, dim=-1)
