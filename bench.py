@@ -234,16 +234,15 @@ def run_gpu_arm(args):
     def step(i: int, timed: bool):
         s = sets[i % N_BUFFER_SETS]
         q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
+        # dynamic LoRA: the low-rank term is stored first, the int8 GEMM adds onto it in its epilogue
+        lora_y = F.lora_up(F.lora_down(s["x"], s["lora"][0]), s["lora"][1]) if s["lora"] is not None else None
         if timed:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype)
+        y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype, add_into=lora_y)
         if timed:
             e1.record()
             gemm_events.append((e0, e1))
-        if s["lora"] is not None:
-            t = F.lora_down(s["x"], s["lora"][0])
-            F.lora_up_add_(y, t, s["lora"][1])
         return y
 
     launches_per_step = 2 + (2 if shape.lora_rank else 0)
@@ -279,9 +278,12 @@ def run_gpu_arm(args):
     def e2e_step(i: int):
         s = sets[i % N_BUFFER_SETS]
         xd = s["x_host"].to(dev, non_blocking=True)
-        y = F.linear_forward(xd, s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard)
         if s["lora"] is not None:
-            F.lora_up_add_(y, F.lora_down(xd, s["lora"][0]), s["lora"][1])
+            q, xs = F.quantize_rowwise(xd, hadamard=shape.hadamard)
+            y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype,
+                              add_into=F.lora_up(F.lora_down(xd, s["lora"][0]), s["lora"][1]))
+        else:
+            y = F.linear_forward(xd, s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard)
         s["y_host"].copy_(y, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 20))

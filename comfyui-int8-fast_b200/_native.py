@@ -42,6 +42,8 @@ _PROTOTYPES = {
                                 c_void_p]),
     "i8f_linear_w8a8": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
                                 c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "i8f_linear_w8a8_add": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                    c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "i8f_linear_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "i8f_linear_forward": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                    c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p,
@@ -50,6 +52,8 @@ _PROTOTYPES = {
                                           c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "i8f_lora_down": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                               c_int64, c_void_p]),
+    "i8f_lora_up": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
+                            c_int64, c_void_p]),
     "i8f_lora_up_add": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                                 c_int64, c_void_p]),
     "i8f_lora_merge_sr": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int,

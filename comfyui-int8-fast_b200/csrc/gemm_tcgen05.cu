@@ -60,7 +60,9 @@ struct GemmParams {
     int bias_dtype;
     int epi_mode;
     int epi_order;
+    int add_existing;  // dequant mode: out = round(round(result) + out) (a LoRA term already stored in out)
     int vec_ok;  // out pointer / pitch allow 16-byte row-segment stores
+    int tma_out; // 16-bit output leaves through shared memory and TMA stores (needs vec_ok)
     int* status;
 };
 
@@ -74,7 +76,8 @@ struct Cfg {
     static constexpr int kTmemCols = 2 * BN;  // 512, 256 or 128: powers of two >= 32
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kEpiBytes = 4 * 2 * BN * 4;  // per epilogue warp: BN column scales + BN biases (fp32)
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kEpiBytes + 1024;  // + alignment slack
+    static constexpr int kOutStageBytes = 4 * 2 * 2048;  // per epilogue warp: two 32-row x 64-byte output chunks
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kEpiBytes + kOutStageBytes + 1024;  // + slack
     static constexpr int kTileM = PAIR ? 2 * kBM : kBM;
 };
 
@@ -171,13 +174,47 @@ __device__ __forceinline__ void load_row32(const GemmParams& p, long long row, i
     }
 }
 
-// One 32-column chunk of one accumulator row -> global memory.  `cs` / `cb`
-// point at this chunk's 32 column scales and biases in shared memory (the
-// bias is already rounded to OUT when the reference order asks for it); every
-// lane reads the same address, a broadcast.
+// Existing output values of one 32-column row segment, fetched ahead of use (4 x 16 bytes per thread).
+struct OldChunk {
+    uint4 raw[4];
+    bool valid;   // raw[] holds the segment (full in-range segment, vector path)
+};
+
+__device__ __forceinline__ void prefetch_old(const GemmParams& p, long long row, bool row_ok, int col, OldChunk& o) {
+    o.valid = row_ok && p.vec_ok && col + 32 <= p.N;
+    if (o.valid) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(p.out) + row * p.ldo + col);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) o.raw[g] = s4[g];
+    }
+}
+
 template <int OUT>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, int col, const uint32_t (&v)[32],
-                                               float row_scale, float ws_scalar, const float* cs, const float* cb) {
+__device__ __forceinline__ void old_values(const GemmParams& p, long long row, int col, const OldChunk& o, float (&y)[32]) {
+    if (o.valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t w[4] = {o.raw[g].x, o.raw[g].y, o.raw[g].z, o.raw[g].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[8 * g + 2 * i] = unpack_lo<OUT>(w[i]);
+                y[8 * g + 2 * i + 1] = unpack_hi<OUT>(w[i]);
+            }
+        }
+    } else {
+        load_row32<OUT>(p, row, col, y);
+    }
+}
+
+// One 32-column chunk of one accumulator row.  `cs` / `cb` point at this chunk's 32 column scales and
+// biases in shared memory (the bias is already rounded to OUT when the reference order asks for it);
+// every lane reads the same address, a broadcast.  The result goes either straight to global memory or,
+// when `stage` is non-zero, into this warp's shared-memory staging chunk (row = lane, 64 bytes per row,
+// 16-byte pieces XOR-swizzled with (row >> 1) & 3 as the TMA 64-byte swizzle expects).
+template <int OUT>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, bool row_ok, int col,
+                                               const uint32_t (&v)[32], float row_scale, float ws_scalar, const float* cs,
+                                               const float* cb, const OldChunk& old, uint32_t stage, int lane) {
     float y[32];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
@@ -205,15 +242,38 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
                 for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], cb[j]);
             }
         }
+        if (p.add_existing && row_ok) {
+            float prev[32];
+            old_values<OUT>(p, row, col, old, prev);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), prev[j]);
+        }
     } else if (p.epi_mode == kEpiCast) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
     } else {  // kEpiAccum: out = round(out + round(acc))
-        load_row32<OUT>(p, row, col, y);
+        if (row_ok) old_values<OUT>(p, row, col, old, y);
+        else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], round_out<OUT>(__uint_as_float(v[j])));
     }
-    store_row32<OUT>(p, row, col, y);
+    if (stage != 0) {
+        const uint32_t row_addr = stage + static_cast<uint32_t>(lane) * 64u;
+        const uint32_t x = static_cast<uint32_t>(lane >> 1) & 3u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const uint32_t a = row_addr + ((static_cast<uint32_t>(g) ^ x) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<OUT>(y[8 * g + 0], y[8 * g + 1])),
+                         "r"(pack2<OUT>(y[8 * g + 2], y[8 * g + 3])), "r"(pack2<OUT>(y[8 * g + 4], y[8 * g + 5])),
+                         "r"(pack2<OUT>(y[8 * g + 6], y[8 * g + 7]))
+                         : "memory");
+        }
+    } else if (row_ok) {
+        store_row32<OUT>(p, row, col, y);
+    }
 }
 
 __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long row, int col, const uint32_t (&v)[32]) {
@@ -231,7 +291,8 @@ __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long r
 
 template <int KIND, int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmOut, const GemmParams p) {
     using C = Cfg<BN, PAIR>;
     constexpr int kElemsPerStage = (KIND == kKindI8) ? kStageRowBytes : kStageRowBytes / 2;
     constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, C::kTileM, BN)
@@ -251,6 +312,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + kBarOff + 16 * C::kStages + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + kBarOff + 16 * C::kStages + 36);
     float* epi_smem = reinterpret_cast<float*>(gen_base + kBarOff + C::kBarrierBytes);
+    const uint32_t out_stage0 = smem_base + kBarOff + C::kBarrierBytes + C::kEpiBytes;  // 1024-byte aligned
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -271,6 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_proxy_async_smem();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (p.tma_out) tma_prefetch_desc(&tmOut);
     }
     if (warp == 1) {
         if constexpr (PAIR) tmem_alloc_pair<C::kTmemCols>(tmem_slot);
@@ -382,6 +445,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool has_bias = dequant && p.bias != nullptr;
         const float ws_scalar = (dequant && !per_ch) ? __ldg(p.w_scale) : 0.f;
         const uint32_t accempty_leader = PAIR ? mapa_cluster(accempty0, 0) : accempty0;
+        const bool need_old = (dequant && p.add_existing) || p.epi_mode == kEpiAccum;
+        const bool tma_out = p.tma_out != 0;
+        const uint32_t out_stage = out_stage0 + static_cast<uint32_t>(warp - 2) * 4096u;
+        uint32_t out_chunk = 0;
         for (int t = tile_first; t < num_tiles; t += tile_step) {
             int m_blk, n_blk;
             tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
@@ -401,24 +468,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
-            tc_fence_after_sync();
             const long long row = static_cast<long long>(m_blk) * C::kTileM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+            const long long warp_row0 = row - lane;
             const bool row_ok = row < p.M;
             const float row_scale = (dequant && row_ok) ? __ldg(p.a_scale + row) : 0.f;
+            OldChunk old_next;
+            old_next.valid = false;
+            if (need_old) prefetch_old(p, row, row_ok, n_blk * BN, old_next);   // in flight while the MMAs finish
+            if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
+            tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
+                const int col = n_blk * BN + c * 32;
+                if (col >= p.N) break;                      // uniform over the CTA
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + c * 32, v);
+                const OldChunk old_cur = old_next;
+                if (need_old && c + 1 < BN / 32 && col + 32 < p.N) prefetch_old(p, row, row_ok, col + 32, old_next);
+                uint32_t stage = 0;
+                if (tma_out) {
+                    stage = out_stage + static_cast<uint32_t>(out_chunk & 1) * 2048u;
+                    // the store that last read this staging chunk (two chunks ago) must be done with it
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                }
                 tmem_ld_wait();
-                const int col = n_blk * BN + c * 32;
-                if (row_ok && col < p.N) {
-                    if (p.epi_mode == kEpiI32) store_i32_row32(p, row, col, v);
-                    else if (p.out_dtype == I8F_BF16)
-                        epilogue_chunk<I8F_BF16>(p, row, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32);
-                    else
-                        epilogue_chunk<I8F_F16>(p, row, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32);
+                if (p.epi_mode == kEpiI32) {
+                    if (row_ok) store_i32_row32(p, row, col, v);
+                } else if (p.out_dtype == I8F_BF16) {
+                    epilogue_chunk<I8F_BF16>(p, row, row_ok, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32,
+                                             old_cur, stage, lane);
+                } else {
+                    epilogue_chunk<I8F_F16>(p, row, row_ok, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32,
+                                            old_cur, stage, lane);
+                }
+                if (tma_out) {
+                    fence_proxy_async_smem();               // generic-proxy writes -> visible to the TMA engine
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmOut, stage, col, static_cast<int>(warp_row0));   // rows / columns past M, N are clipped
+                        tma_store_commit();
+                    }
+                    ++out_chunk;
                 }
             }
             tc_fence_before_sync();
@@ -430,6 +522,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             buf ^= 1;
             if (buf == 0) acc_phase ^= 1u;
         }
+        if (tma_out && lane == 0) tma_store_wait_all<0>();   // shared memory must outlive the last store's reads
     }
 
     // common teardown (also reached after an aborted wait)
@@ -488,6 +581,21 @@ int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, 
     return I8F_OK;
 }
 
+// Output [rows, cols] of 16-bit elements, box = 32 columns x 32 rows (one epilogue warp's chunk), 64-byte swizzle.
+int make_out_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld_elems) {
+    EncodeFn enc = get_encode_fn();
+    I8F_REQUIRE(enc != nullptr, I8F_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    I8F_REQUIRE(r == CUDA_SUCCESS, I8F_ERR_CUDA, "cuTensorMapEncodeTiled(out) failed with CUresult %d", static_cast<int>(r));
+    return I8F_OK;
+}
+
 int current_device() {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -510,6 +618,16 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     if (rc != I8F_OK) return rc;
     rc = make_operand_map(&tmB, KIND, b, N, K, ldb, C::kBRows);
     if (rc != I8F_OK) return rc;
+    static const int no_tma_store = [] {
+        const char* e = getenv("I8F_GEMM_DIRECT_STORE");
+        return (e != nullptr && e[0] == '1') ? 1 : 0;
+    }();
+    CUtensorMap tmOut{};
+    p.tma_out = (p.epi_mode != kEpiI32 && p.vec_ok && !no_tma_store) ? 1 : 0;
+    if (p.tma_out) {
+        rc = make_out_map(&tmOut, p.out, M, N, p.ldo);
+        if (rc != I8F_OK) return rc;
+    }
     const int esz = KIND == kKindI8 ? 1 : 2;
     const int k_per_stage = kStageRowBytes / esz;
     p.M = static_cast<int>(M);
@@ -564,7 +682,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     } else {
         cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()), 1, 1);
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, p);
     if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "gemm_tcgen05_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tcgen05_kernel");
 }
@@ -621,9 +739,10 @@ int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, 
     return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
 }
 
-int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
-                    const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out, int out_dtype,
-                    int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
+static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                            const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out,
+                            int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order,
+                            int add_existing, void* stream) {
     int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
     if (rc != I8F_OK) return rc;
     I8F_REQUIRE(a_scale != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL scale pointer");
@@ -645,8 +764,23 @@ int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const in
     p.bias_dtype = bias_dtype;
     p.epi_mode = kEpiDequant;
     p.epi_order = epilogue_order;
+    p.add_existing = add_existing;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
     return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+}
+
+int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                    const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out, int out_dtype,
+                    int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
+    return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
+                            epilogue_order, 0, stream);
+}
+
+int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                        const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out,
+                        int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
+    return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
+                            epilogue_order, 1, stream);
 }
 
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K) {
@@ -689,6 +823,23 @@ int i8f_lora_down(const void* x, int64_t ldx, const void* lora_a, int64_t lda, v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == I8F_BF16) return launch_gemm_auto<kKindBF16>(x, ldx, lora_a, lda, M, r, K, p, st);
     return launch_gemm_auto<kKindF16>(x, ldx, lora_a, lda, M, r, K, p, st);
+}
+
+int i8f_lora_up(const void* t, int64_t ldt, const void* lora_b, int64_t ldb, void* y, int64_t ldy, int dtype, int64_t M,
+                int64_t N, int64_t r, void* stream) {
+    I8F_REQUIRE(dtype == I8F_BF16 || dtype == I8F_F16, I8F_ERR_UNSUPPORTED, "dtype must be bf16 or f16");
+    int rc = check_operands(t, ldt, lora_b, ldb, 2, M, N, r);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(y != nullptr && ldy >= N, I8F_ERR_INVALID_ARG, "bad output");
+    GemmParams p{};
+    p.out = y;
+    p.ldo = ldy;
+    p.out_dtype = dtype;
+    p.epi_mode = kEpiCast;
+    p.vec_ok = aligned16(y) && (ldy % 8 == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == I8F_BF16) return launch_gemm_auto<kKindBF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
+    return launch_gemm_auto<kKindF16>(t, ldt, lora_b, ldb, M, N, r, p, st);
 }
 
 int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb, void* y, int64_t ldy, int dtype,

@@ -80,6 +80,59 @@ __device__ __forceinline__ int swz(int col) {
     return ((chunk ^ ((chunk >> 3) & 1)) << 2) | (col & 3);
 }
 
+// Shared tail of both merge kernels.  acc[i][c] is the un-scaled delta of row n_first + i, columns
+// kc..kc+7 (the thread's 2 x 8 patch; 16 adjacent lanes hold one 128-column block of a row).
+template <bool HAD>
+__device__ __forceinline__ void merge_tail(float (&acc)[2][8], int8_t* __restrict__ w, long long ldw,
+                                           const float* __restrict__ w_scale, int ws_mode, int n_first, int row_end, int kc,
+                                           int K, int lane, float lora_scale, const float* __restrict__ uniforms,
+                                           uint32_t key0, uint32_t key1, int w_vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], lora_scale);
+        if constexpr (HAD) {
+            wht128_lanes16(acc[i], lane);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], kNormF32);
+        }
+        const int n = n_first + i;
+        if (n >= row_end || kc >= K) continue;
+        const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
+        float u[8];
+        if (uniforms != nullptr) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) u[c] = (kc + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + kc + c) : 1.f;
+        } else {
+            const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), key0, key1);
+            const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, key0, key1);
+            u[0] = u01(ra.x); u[1] = u01(ra.y); u[2] = u01(ra.z); u[3] = u01(ra.w);
+            u[4] = u01(rb.x); u[5] = u01(rb.y); u[6] = u01(rb.z); u[7] = u01(rb.w);
+        }
+        int8_t* wp = w + static_cast<long long>(n) * ldw + kc;
+        if (w_vec_ok && kc + 8 <= K) {
+            uint2 old = *reinterpret_cast<const uint2*>(wp);
+            uint32_t ow[2] = {old.x, old.y};
+            uint32_t nw[2] = {0u, 0u};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int wo = static_cast<int>(static_cast<int8_t>((ow[c >> 2] >> (8 * (c & 3))) & 0xFFu));
+                const int s = max(-128, min(127, wo + sr_round(acc[i][c], ws, u[c])));
+                nw[c >> 2] |= (static_cast<uint32_t>(s) & 0xFFu) << (8 * (c & 3));
+            }
+            *reinterpret_cast<uint2*>(wp) = make_uint2(nw[0], nw[1]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (kc + c < K) {
+                    const int s = max(-128, min(127, static_cast<int>(wp[c]) + sr_round(acc[i][c], ws, u[c])));
+                    wp[c] = static_cast<int8_t>(s);
+                }
+            }
+        }
+    }
+}
+
 template <bool HAD>
 __global__ void __launch_bounds__(kThreads)
 lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict__ w_scale, int ws_mode,
@@ -129,50 +182,104 @@ lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict
                 acc[1][c] = __fadd_rn(acc[1][c], __fmul_rn(ub, d[c]));
             }
         }
+        merge_tail<HAD>(acc, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, key0, key1,
+                        w_vec_ok);
+    }
+}
+
+// Tensor-core form for 16-bit factors.  The rank-r product of a 32 x 128 tile runs on mma.sync
+// (m16n8k16, fp32 accumulate) from shared memory: `down` is staged once per CTA transposed as
+// [128 columns][r] so that consecutive rank indices are adjacent (B fragments), `up` rows as [32][r]
+// (A fragments); rows are padded by 8 elements, which makes the 32-bit fragment loads conflict free.
+// The accumulators go through shared memory into the 2 x 8 per-thread patches of the common tail.
+// Tensor-core accumulation is not the sequential fp32 sum of the exact kernel, so a delta can differ in
+// its last place; after stochastic rounding that shows up as a +-1 difference in about one weight per
+// million.  This is what makes the merge bandwidth- instead of FMA-bound.
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2], bool is_bf16) {
+    if (is_bf16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+    }
+}
+
+constexpr int kAccStride = 132;  // floats per row of the accumulator tile in shared memory
+
+template <bool HAD>
+__global__ void __launch_bounds__(kThreads)
+lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict__ w_scale, int ws_mode,
+                     const unsigned short* __restrict__ up, long long ldup, const unsigned short* __restrict__ down,
+                     long long lddown, int is_bf16, int N, int K, int r, int r16, float lora_scale,
+                     const float* __restrict__ uniforms, unsigned long long seed, int rows_per_cta, int w_vec_ok) {
+    extern __shared__ float smem[];
+    const int rp = r16 + 8;                                        // padded rank (16-bit elements per row)
+    float* s_acc = smem;                                            // [32][kAccStride] fp32
+    unsigned short* s_downT = reinterpret_cast<unsigned short*>(smem + kRowsPerIter * kAccStride);  // [128][rp]
+    unsigned short* s_up = s_downT + 128 * rp;                      // [32][rp]
+    const int k0 = blockIdx.x * 128;
+    for (int idx = threadIdx.x; idx < r16 * 128; idx += kThreads) {
+        const int j = idx >> 7, c = idx & 127;                      // coalesced along the columns of `down`
+        s_downT[c * rp + j] = (j < r && k0 + c < K) ? down[static_cast<long long>(j) * lddown + k0 + c] : 0;
+    }
+    const int row_begin = blockIdx.y * rows_per_cta;
+    const int row_end = min(N, row_begin + rows_per_cta);
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int wm = (warp & 1) * 16;                                 // this warp's 16 rows ...
+    const int wn = (warp >> 1) * 32;                                // ... and 32 columns of the tile
+    const int kc = k0 + tc * 8;
+    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
+
+    for (int n0 = row_begin; n0 < row_end; n0 += kRowsPerIter) {
+        __syncthreads();                                            // previous tile fully consumed (s_up, s_acc)
+        for (int idx = threadIdx.x; idx < kRowsPerIter * r16; idx += kThreads) {
+            const int rr = idx / r16, j = idx - rr * r16;
+            s_up[rr * rp + j] = (j < r && n0 + rr < row_end) ? up[static_cast<long long>(n0 + rr) * ldup + j] : 0;
+        }
+        __syncthreads();
+        float d[4][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], lora_scale);
-            if constexpr (HAD) {
-                wht128_lanes16(acc[i], lane);
+            for (int e = 0; e < 4; ++e) d[nt][e] = 0.f;
+        for (int kk = 0; kk < r16; kk += 16) {
+            uint32_t a[4];
+            const unsigned short* ar = s_up + (wm + g) * rp + kk + 2 * t4;
+            a[0] = *reinterpret_cast<const uint32_t*>(ar);
+            a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * rp);
+            a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * rp + 8);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) acc[i][c] = __fmul_rn(acc[i][c], kNormF32);
-            }
-            const int n = n0 + 2 * tr + i;
-            if (n >= row_end || kc >= K) continue;
-            const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
-            float u[8];
-            if (uniforms != nullptr) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) u[c] = (kc + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + kc + c) : 1.f;
-            } else {
-                const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), key0, key1);
-                const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, key0, key1);
-                u[0] = u01(ra.x); u[1] = u01(ra.y); u[2] = u01(ra.z); u[3] = u01(ra.w);
-                u[4] = u01(rb.x); u[5] = u01(rb.y); u[6] = u01(rb.z); u[7] = u01(rb.w);
-            }
-            int8_t* wp = w + static_cast<long long>(n) * ldw + kc;
-            if (w_vec_ok && kc + 8 <= K) {
-                uint2 old = *reinterpret_cast<const uint2*>(wp);
-                uint32_t ow[2] = {old.x, old.y};
-                uint32_t nw[2] = {0u, 0u};
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int wo = static_cast<int>(static_cast<int8_t>((ow[c >> 2] >> (8 * (c & 3))) & 0xFFu));
-                    const int s = max(-128, min(127, wo + sr_round(acc[i][c], ws, u[c])));
-                    nw[c >> 2] |= (static_cast<uint32_t>(s) & 0xFFu) << (8 * (c & 3));
-                }
-                *reinterpret_cast<uint2*>(wp) = make_uint2(nw[0], nw[1]);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    if (kc + c < K) {
-                        const int s = max(-128, min(127, static_cast<int>(wp[c]) + sr_round(acc[i][c], ws, u[c])));
-                        wp[c] = static_cast<int8_t>(s);
-                    }
-                }
+            for (int nt = 0; nt < 4; ++nt) {
+                uint32_t b[2];
+                const unsigned short* br = s_downT + (wn + nt * 8 + g) * rp + kk + 2 * t4;
+                b[0] = *reinterpret_cast<const uint32_t*>(br);
+                b[1] = *reinterpret_cast<const uint32_t*>(br + 8);
+                mma_16816(d[nt], a, b, is_bf16 != 0);
             }
         }
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float* o = s_acc + (wm + g) * kAccStride + wn + nt * 8 + 2 * t4;
+            *reinterpret_cast<float2*>(o) = make_float2(d[nt][0], d[nt][1]);
+            *reinterpret_cast<float2*>(o + 8 * kAccStride) = make_float2(d[nt][2], d[nt][3]);
+        }
+        __syncthreads();
+        float acc[2][8];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float4 lo = *reinterpret_cast<const float4*>(s_acc + (2 * tr + i) * kAccStride + tc * 8);
+            const float4 hi = *reinterpret_cast<const float4*>(s_acc + (2 * tr + i) * kAccStride + tc * 8 + 4);
+            acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = lo.z; acc[i][3] = lo.w;
+            acc[i][4] = hi.x; acc[i][5] = hi.y; acc[i][6] = hi.z; acc[i][7] = hi.w;
+        }
+        merge_tail<HAD>(acc, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, key0, key1,
+                        w_vec_ok);
     }
 }
 
@@ -226,8 +333,14 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
     I8F_REQUIRE(ldw >= K && ldup >= r && lddown >= K, I8F_ERR_INVALID_ARG, "pitch smaller than the row length");
     I8F_REQUIRE(!hadamard128 || K % 128 == 0, I8F_ERR_UNSUPPORTED, "Hadamard rotation needs K %% 128 == 0");
     I8F_REQUIRE(N < (1LL << 31) && K < (1LL << 31), I8F_ERR_UNSUPPORTED, "dimension too large");
-    const size_t smem = (static_cast<size_t>(r) * 128 + static_cast<size_t>(kRowsPerIter) * (r + 1)) * sizeof(float);
-    I8F_REQUIRE(smem <= 200 * 1024, I8F_ERR_UNSUPPORTED, "rank %lld too large for one pass (max 320)", (long long)r);
+    // 16-bit factors with the in-kernel counter RNG take the tensor-core kernel; fp32 factors, and any call that
+    // supplies its own uniforms (the bit-exact parity mode), take the sequential fp32 kernel
+    const bool tensor_path = factor_dtype != I8F_F32 && uniforms == nullptr && r > 0 && ldup % 2 == 0 && lddown % 2 == 0;
+    const int r16 = static_cast<int>((r + 15) / 16 * 16);
+    const size_t smem = tensor_path
+        ? static_cast<size_t>(kRowsPerIter) * kAccStride * sizeof(float) + static_cast<size_t>(128 + kRowsPerIter) * (r16 + 8) * 2
+        : (static_cast<size_t>(r) * 128 + static_cast<size_t>(kRowsPerIter) * (r + 1)) * sizeof(float);
+    I8F_REQUIRE(smem <= 200 * 1024, I8F_ERR_UNSUPPORTED, "rank %lld too large for one pass", (long long)r);
     const int col_blocks = static_cast<int>((K + 127) / 128);
     // enough row bands to fill the GPU a few times over, each band a multiple of 32 rows
     int bands = (148 * 4 + col_blocks - 1) / col_blocks;
@@ -241,6 +354,20 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
     const int w_vec_ok = ((reinterpret_cast<uintptr_t>(w) & 7u) == 0 && ldw % 8 == 0) ? 1 : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(col_blocks, bands);
+    if (tensor_path) {
+        auto launch_tc = [&](auto kern) -> int {
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+                if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            }
+            kern<<<grid, kThreads, smem, st>>>(w, ldw, w_scale, w_scale_mode, static_cast<const unsigned short*>(up), ldup,
+                                               static_cast<const unsigned short*>(down), lddown,
+                                               factor_dtype == I8F_BF16 ? 1 : 0, static_cast<int>(N), static_cast<int>(K),
+                                               static_cast<int>(r), r16, lora_scale, uniforms, seed, rows_per_cta, w_vec_ok);
+            return check_launch("lora_merge_tc_kernel");
+        };
+        return hadamard128 ? launch_tc(lora_merge_tc_kernel<true>) : launch_tc(lora_merge_tc_kernel<false>);
+    }
     auto launch = [&](auto kern) -> int {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -111,8 +111,12 @@ def gemm_i8_i32(a: Tensor, w: Tensor) -> Tensor:
 
 
 def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype,
-                order: int = nat.EPI_PYTORCH) -> Tensor:
-    """Dequantising int8 GEMM from pre-quantised activations."""
+                order: int = nat.EPI_PYTORCH, add_into: Tensor | None = None) -> Tensor:
+    """Dequantising int8 GEMM from pre-quantised activations.
+
+    With `add_into` ([M,N], out_dtype, unit inner stride) the result is added onto what that tensor holds
+    (out = round(round(result) + add_into)), in place, and `add_into` is returned.
+    """
     nat.require_device(q.device)
     q, w = _rows(q), _rows(w)
     M, K = q.shape
@@ -122,12 +126,16 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
         raise ValueError(f"per-channel weight scale has {ws.numel()} entries for N={N}")
     if bias is not None:
         bias = bias.to(q.device).contiguous()
-    out = torch.empty((M, N), dtype=out_dtype, device=q.device)
+    if add_into is not None:
+        if add_into.shape != (M, N) or add_into.dtype != out_dtype or add_into.stride(1) != 1:
+            raise ValueError("add_into must be [M,N] in out_dtype with unit inner stride")
+        out, fn, what = add_into, nat.load().i8f_linear_w8a8_add, "i8f_linear_w8a8_add"
+    else:
+        out, fn, what = torch.empty((M, N), dtype=out_dtype, device=q.device), nat.load().i8f_linear_w8a8, "i8f_linear_w8a8"
     if M and N:
-        nat.check(nat.load().i8f_linear_w8a8(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w),
-                                             nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
-                                             nat.ptr(out), _code(out_dtype), N, M, N, K, order,
-                                             nat.current_stream(q.device)), "i8f_linear_w8a8")
+        nat.check(fn(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w), nat.ptr(ws), mode, nat.ptr(bias),
+                     _code(bias.dtype) if bias is not None else 0, nat.ptr(out), _code(out_dtype), _ld(out), M, N, K, order,
+                     nat.current_stream(q.device)), what)
     return out
 
 
@@ -196,6 +204,21 @@ def lora_down(x: Tensor, lora_a: Tensor) -> Tensor:
         nat.check(nat.load().i8f_lora_down(nat.ptr(x), _ld(x), nat.ptr(lora_a), _ld(lora_a), nat.ptr(t), r, _code(x.dtype),
                                            M, K, r, nat.current_stream(x.device)), "i8f_lora_down")
     return t
+
+
+def lora_up(t: Tensor, lora_b: Tensor) -> Tensor:
+    """y [M,N] = round(t [M,r] @ lora_b [N,r]^T) in t's dtype."""
+    nat.require_device(t.device)
+    t, lora_b = _rows(t), _rows(lora_b.to(t.dtype))
+    M, r = t.shape
+    N = lora_b.shape[0]
+    y = torch.empty((M, N), dtype=t.dtype, device=t.device)
+    if M and N and r:
+        nat.check(nat.load().i8f_lora_up(nat.ptr(t), _ld(t), nat.ptr(lora_b), _ld(lora_b), nat.ptr(y), N, _code(t.dtype),
+                                         M, N, r, nat.current_stream(t.device)), "i8f_lora_up")
+    elif M and N:
+        y.zero_()
+    return y
 
 
 def lora_up_add_(y: Tensor, t: Tensor, lora_b: Tensor) -> Tensor:

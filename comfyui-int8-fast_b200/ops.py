@@ -538,21 +538,27 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 lora_in = x2
 
                 with torch.cuda.device(x.device):
-                    if rows > SMALL_BATCH_ROWS:
-                        if has_lora and self._use_quarot and Int8TensorwiseOps.lora_uses_rotated_input:
+                    if rows > SMALL_BATCH_ROWS and has_lora:
+                        # low-rank term first (stored rounded, as the reference's lora_y), then the int8 GEMM adds
+                        # onto it in its epilogue: y = round(round(dequant + bias) + lora_y)
+                        if self._use_quarot and Int8TensorwiseOps.lora_uses_rotated_input:
                             q, qs, lora_in = F.quantize_rowwise(x2, hadamard=True, return_rotated=True)
-                            y = F.linear_w8a8(q, qs, weight, w_scale, bias, compute_dtype)
                         else:
-                            y = F.linear_forward(x2, weight, w_scale, bias, compute_dtype, hadamard=self._use_quarot,
-                                                 workspace=self._workspace_for(rows, x.device))
+                            q, qs = F.quantize_rowwise(x2, hadamard=self._use_quarot)
+                        lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
+                        lora_y = F.lora_up(F.lora_down(lora_in, lora_a), lora_b)
+                        y = F.linear_w8a8(q, qs, weight, w_scale, bias, compute_dtype, add_into=lora_y)
+                    elif rows > SMALL_BATCH_ROWS:
+                        y = F.linear_forward(x2, weight, w_scale, bias, compute_dtype, hadamard=self._use_quarot,
+                                             workspace=self._workspace_for(rows, x.device))
                     else:
                         if self._use_quarot:
                             lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)
                         w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
                         y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
-                    if has_lora:
-                        lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
-                        F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)
+                        if has_lora:
+                            lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
+                            F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)
 
                 if need_cast:
                     uncast_bias_weight(self, weight, bias, stream)

@@ -86,7 +86,7 @@ int i8f_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t 
 /* Quantisation with one scale for the whole tensor (weights).
  *   scale_out[0] = max(absmax(x)/127, 1e-30); q as above.
  * `scratch` is 4 bytes of device memory owned by the caller (absmax exchange).
- * hadamard128 rotates each row block in fp32 first (x_dtype must be I8F_F32).
+ * hadamard128 rotates each row block in fp32 first (any x_dtype; values are converted to fp32).
  * Replaces quantize_int8_tensorwise (int8_quant.py:23-26) and rotate_weight
  * (quarot.py:42-70). */
 int i8f_quant_tensorwise(const void* x, int x_dtype, int64_t N, int64_t K, int64_t ldx,
@@ -117,6 +117,17 @@ int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale,
                     const void* bias, int bias_dtype,
                     void* out, int out_dtype, int64_t ldo,
                     int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
+
+/* Same as i8f_linear_w8a8, then adds what `out` held on entry:
+ *   out = round(round(dequant (+bias)) + out_before)
+ * With out_before = round(t @ lora_b^T) from i8f_lora_up this is the dynamic-LoRA forward
+ * y + lora_y.to(y.dtype) of int8_quant.py:763-774 with the same three roundings, and the read of the
+ * LoRA term overlaps the tensor-core main loop instead of costing a separate pass over y. */
+int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale,
+                        const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                        const void* bias, int bias_dtype,
+                        void* out, int out_dtype, int64_t ldo,
+                        int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
 /* Bytes of caller-owned workspace i8f_linear_forward needs for an [M,K] input. */
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K);
@@ -162,6 +173,11 @@ int i8f_linear_forward_static(const void* x, int x_dtype, int64_t ldx, int hadam
  * Replaces F.linear(x_2d, lora_A) at int8_quant.py:768. */
 int i8f_lora_down(const void* x, int64_t ldx, const void* lora_a, int64_t lda,
                   void* t, int64_t ldt, int dtype, int64_t M, int64_t K, int64_t r, void* stream);
+
+/* Dynamic-LoRA up projection alone: y [M,N] = round(t [M,r] @ lora_b [N,r]^T) in `dtype`.
+ * Replaces F.linear(lora_x, lora_B) at int8_quant.py:769; feed the result to i8f_linear_w8a8_add. */
+int i8f_lora_up(const void* t, int64_t ldt, const void* lora_b, int64_t ldb,
+                void* y, int64_t ldy, int dtype, int64_t M, int64_t N, int64_t r, void* stream);
 
 /* Dynamic-LoRA up projection and add: y [M,N] = round(y + round(t [M,r] @ lora_b [N,r]^T)).
  * Replaces int8_quant.py:769-774. */

