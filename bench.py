@@ -496,12 +496,136 @@ def run_dit(args):
         "gpu_launches": 2 * n_int8 * steps * world, "clocks": clocks, "device_status": status, "output_finite": finite}))
 
 
+# ------------------------------------------- column-parallel sweep (config 4)
+NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
+
+
+def run_column_parallel(args):
+    """W8A8 linear K=4096, N=16384 split over the ranks by output channel; every rank quantises the full x, runs
+    its slice and the bf16 [M, N/P] blocks are all-gathered (NCCL).  One line with a result per M."""
+    import torch
+    import __graft_entry__ as g
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    K, N = 4096, 16384
+    m_sweep = [1024, 4096, 16384, 32768]
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        import __graft_entry__ as g2
+        wl = g2.load_package().workloads
+        base, dt = cpu_reference_rate(wl.LinearShape("c4_column_parallel", 4096, K, N, False, True, False), args.steps,
+                                      args.warmup, budget_s=40.0)
+        print(json.dumps({"impl": "reference", "metric": "w8a8_linear_int8_throughput", "value": base["value"], "unit": "TOPS",
+                          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+                          "data": "synthetic", "config": {"workload": "c4_column_parallel", "K": K, "N": N, "M": 4096},
+                          "cpu_baseline": base, "gpu_launches": 0,
+                          "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = g.load_package()
+    F, par, wl = pkg.functional, pkg.parallel, pkg.workloads
+    w = wl.weight_fp32(N, K, seed=4)
+    b0, e0_ = par.shard_bounds(N, world, rank)
+    wq, ws = F.quantize_weight_rows(w[b0:e0_].to(dev))
+    n_local = e0_ - b0
+    steps = min(args.steps, 50)
+    results = []
+    for M in m_sweep:
+        x = wl.activation(M, K, seed=40).to(dev)          # same bits on every rank
+        gathered = torch.empty((world * M, n_local), dtype=torch.bfloat16, device=dev)   # [P, M, N/P] blocks
+        full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+
+        def step(relayout: bool):
+            q, xs = F.quantize_rowwise(x)
+            y = F.linear_w8a8(q, xs, wq, ws, None, torch.bfloat16)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, y)
+                if relayout:
+                    full.view(M, world, n_local).copy_(gathered.view(world, M, n_local).transpose(0, 1))
+            return y
+
+        def timed(relayout: bool):
+            for _ in range(3):
+                step(relayout)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                step(relayout)
+            b.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        ms_blocks = timed(False)
+        ms_full = timed(True) if world > 1 else ms_blocks
+        ms_fused, fused_equal = None, None
+        if world > 1 and n_local % 32 == 0:
+            try:
+                shard = par.ColumnShard(wq, ws, None, b0, e0_, N)
+                fused = par.FusedColumnParallelOutput(M, N, torch.bfloat16, dev)
+                step_nccl = step
+
+                def step(relayout: bool):       # noqa: F811 - same timing harness, fused kernel
+                    return fused.forward(x, shard)
+
+                ms_fused = timed(False)
+                y_all = fused.forward(x, shard)
+                torch.cuda.synchronize()
+                step = step_nccl
+                step(True)
+                torch.cuda.synchronize()
+                fused_equal = bool(torch.equal(y_all, full))
+                del fused
+            except Exception as e:  # noqa: BLE001
+                ms_fused, fused_equal = None, f"unavailable: {e!r}"
+        # parity of the gathered result with the unsharded computation on rank 0's slice of columns
+        ops = 2.0 * M * N * K
+        comm_bytes = 2.0 * M * N * (world - 1) / world
+        nvlink_ms = comm_bytes / (NVLINK_PEER_GBS * 1e9) * 1e3
+        results.append({"M": M, "ms_fused_epilogue_scatter": ms_fused, "fused_equals_nccl_result": fused_equal,
+                        "frac_of_nvlink_roofline_fused": (nvlink_ms / ms_fused) if ms_fused else None,
+                        "ms_blocks_layout": ms_blocks, "ms_row_major_layout": ms_full,
+                        "tops": ops / (ms_blocks * 1e-3) / 1e12, "allgather_bytes_in_per_gpu": comm_bytes,
+                        "nvlink_roofline_ms": nvlink_ms, "frac_of_nvlink_roofline": (nvlink_ms / ms_blocks) if world > 1 else None})
+        del x, gathered, full
+    status = pkg._native.device_status()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ref = next(r for r in results if r["M"] == 4096)
+    print(json.dumps({"metric": "w8a8_linear_int8_throughput", "value": ref["tops"], "unit": "TOPS", "n_gpus": world,
+                      "steps": steps, "warmup": 3, "ms_per_step": ref["ms_blocks_layout"], "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                      "config": {"workload": "c4_column_parallel", "K": K, "N": N, "M": 4096, "weight_scale": "per_channel",
+                                 "parallelism": f"column-parallel x{world}, NCCL all-gather of bf16 [M, N/P] blocks",
+                                 "l2": "weights 64 MB / P per rank stay L2-resident across steps (real layers would not)"},
+                      "sweep": results, "gpu_launches": 2 * steps * world * len(m_sweep) * 2, "device_status": status,
+                      "note": "communication-bound by construction: bytes/op ratio is fixed by K; roofline is NVLink, "
+                              f"{NVLINK_PEER_GBS} GB/s per direction per GPU (measured peer copy)"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2", "dit"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c4", "dit"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     args = ap.parse_args()
@@ -509,6 +633,8 @@ def main():
         args.warmup = 3
     if args.workload == "dit":
         run_dit(args)
+    elif args.workload == "c4":
+        run_column_parallel(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -63,7 +63,17 @@ struct GemmParams {
     int add_existing;  // dequant mode: out = round(round(result) + out) (a LoRA term already stored in out)
     int vec_ok;  // out pointer / pitch allow 16-byte row-segment stores
     int tma_out; // 16-bit output leaves through shared memory and TMA stores (needs vec_ok)
+    int n_out;   // number of destinations (tensor maps) every output chunk is stored to
+    int out_col0; // column of the destination matrices at which this launch's block starts
     int* status;
+};
+
+constexpr int kMaxOutputs = 8;
+
+// Tensor maps of the output: one for an ordinary launch; one per destination (this GPU's and its peers' copies of
+// the full activation matrix) when the result block is scattered to several GPUs from the epilogue.
+struct alignas(64) OutMaps {
+    CUtensorMap m[kMaxOutputs];
 };
 
 template <int BN, bool PAIR>
@@ -292,7 +302,7 @@ __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long r
 template <int KIND, int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmOut, const GemmParams p) {
+                    const __grid_constant__ OutMaps outs, const GemmParams p) {
     using C = Cfg<BN, PAIR>;
     constexpr int kElemsPerStage = (KIND == kKindI8) ? kStageRowBytes : kStageRowBytes / 2;
     constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, C::kTileM, BN)
@@ -333,7 +343,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_proxy_async_smem();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        if (p.tma_out) tma_prefetch_desc(&tmOut);
+        if (p.tma_out)
+            for (int d = 0; d < p.n_out; ++d) tma_prefetch_desc(&outs.m[d]);
     }
     if (warp == 1) {
         if constexpr (PAIR) tmem_alloc_pair<C::kTmemCols>(tmem_slot);
@@ -507,7 +518,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     fence_proxy_async_smem();               // generic-proxy writes -> visible to the TMA engine
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&tmOut, stage, col, static_cast<int>(warp_row0));   // rows / columns past M, N are clipped
+                        // rows past M (and, for a single destination, columns past N) are clipped by the TMA unit
+                        for (int d = 0; d < p.n_out; ++d)
+                            tma_store_2d(&outs.m[d], stage, p.out_col0 + col, static_cast<int>(warp_row0));
                         tma_store_commit();
                     }
                     ++out_chunk;
@@ -609,9 +622,17 @@ int sm_count() {
     return cached[dev] > 0 ? cached[dev] : 148;
 }
 
+struct Scatter {
+    void* const* dests;   // base pointers of the destination matrices ([M, n_total], pitch ld elements)
+    int n_dests;
+    int64_t n_total;
+    int64_t ld;
+    int64_t col_offset;
+};
+
 template <int KIND, int BN, bool PAIR>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K, GemmParams p,
-                cudaStream_t st) {
+                cudaStream_t st, const Scatter* scatter = nullptr) {
     using C = Cfg<BN, PAIR>;
     CUtensorMap tmA, tmB;
     int rc = make_operand_map(&tmA, KIND, a, M, K, lda, kBM);
@@ -622,11 +643,24 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
         const char* e = getenv("I8F_GEMM_DIRECT_STORE");
         return (e != nullptr && e[0] == '1') ? 1 : 0;
     }();
-    CUtensorMap tmOut{};
-    p.tma_out = (p.epi_mode != kEpiI32 && p.vec_ok && !no_tma_store) ? 1 : 0;
-    if (p.tma_out) {
-        rc = make_out_map(&tmOut, p.out, M, N, p.ldo);
-        if (rc != I8F_OK) return rc;
+    OutMaps outs{};
+    if (scatter != nullptr) {
+        // one map per destination over the whole [M, n_total] matrix; the block lands at column out_col0
+        p.tma_out = 1;
+        p.n_out = scatter->n_dests;
+        p.out_col0 = static_cast<int>(scatter->col_offset);
+        for (int d = 0; d < scatter->n_dests; ++d) {
+            rc = make_out_map(&outs.m[d], scatter->dests[d], M, scatter->n_total, scatter->ld);
+            if (rc != I8F_OK) return rc;
+        }
+    } else {
+        p.tma_out = (p.epi_mode != kEpiI32 && p.vec_ok && !no_tma_store) ? 1 : 0;
+        p.n_out = p.tma_out;
+        p.out_col0 = 0;
+        if (p.tma_out) {
+            rc = make_out_map(&outs.m[0], p.out, M, N, p.ldo);
+            if (rc != I8F_OK) return rc;
+        }
     }
     const int esz = KIND == kKindI8 ? 1 : 2;
     const int k_per_stage = kStageRowBytes / esz;
@@ -682,7 +716,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     } else {
         cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()), 1, 1);
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmOut, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, outs, p);
     if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "gemm_tcgen05_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tcgen05_kernel");
 }
@@ -692,17 +726,17 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
 // short batches).
 template <int KIND>
 int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
-                     const GemmParams& p, cudaStream_t st) {
+                     const GemmParams& p, cudaStream_t st, const Scatter* scatter = nullptr) {
     static const int force_single = [] {
         const char* e = getenv("I8F_GEMM_SINGLE_CTA");
         return (e != nullptr && e[0] == '1') ? 1 : 0;
     }();
     if (N > 128) {
-        if (M > 128 && !force_single) return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st);
-        return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st);
+        if (M > 128 && !force_single) return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st, scatter);
+        return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
     }
-    if (N > 64) return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st);
-    return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st);
+    if (N > 64) return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
+    return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
 }
 
 int check_operands(const void* a, int64_t lda, const void* b, int64_t ldb, int esz, int64_t M, int64_t N, int64_t K) {
@@ -742,7 +776,7 @@ int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, 
 static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
                             const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out,
                             int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order,
-                            int add_existing, void* stream) {
+                            int add_existing, void* stream, const Scatter* scatter = nullptr) {
     int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
     if (rc != I8F_OK) return rc;
     I8F_REQUIRE(a_scale != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL scale pointer");
@@ -766,7 +800,7 @@ static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, 
     p.epi_order = epilogue_order;
     p.add_existing = add_existing;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
-    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream));
+    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), scatter);
 }
 
 int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
@@ -781,6 +815,26 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale, cons
                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
     return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
                             epilogue_order, 1, stream);
+}
+
+int i8f_linear_w8a8_scatter(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                            const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* const* dests,
+                            int n_dests, int64_t ld_dest, int64_t n_total, int64_t col_offset, int out_dtype, int64_t M,
+                            int64_t N, int64_t K, int epilogue_order, void* stream) {
+    I8F_REQUIRE(dests != nullptr && n_dests >= 1 && n_dests <= kMaxOutputs, I8F_ERR_INVALID_ARG,
+                "n_dests must be 1..%d", kMaxOutputs);
+    I8F_REQUIRE(N % 32 == 0, I8F_ERR_UNSUPPORTED,
+                "the block width N=%lld must be a multiple of 32 (a partial chunk would spill into the neighbour's columns)",
+                (long long)N);
+    I8F_REQUIRE(col_offset >= 0 && col_offset % 8 == 0 && col_offset + N <= n_total && ld_dest >= n_total && ld_dest % 8 == 0,
+                I8F_ERR_INVALID_ARG, "bad destination geometry: col_offset=%lld N=%lld n_total=%lld ld=%lld",
+                (long long)col_offset, (long long)N, (long long)n_total, (long long)ld_dest);
+    for (int d = 0; d < n_dests; ++d)
+        I8F_REQUIRE(dests[d] != nullptr && aligned16(dests[d]), I8F_ERR_ALIGNMENT, "destination %d is NULL or not 16-byte aligned", d);
+    const Scatter sc{dests, n_dests, n_total, ld_dest, col_offset};
+    // `out` / `ldo` of the ordinary path are only used for validation here: point them at the first destination
+    return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, dests[0], out_dtype, ld_dest, M,
+                            N, K, epilogue_order, 0, stream, &sc);
 }
 
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K) {

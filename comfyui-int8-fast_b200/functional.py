@@ -139,6 +139,25 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
     return out
 
 
+def linear_w8a8_scatter(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, dest_ptrs: list[int],
+                        n_total: int, col_offset: int, out_dtype: torch.dtype, order: int = nat.EPI_PYTORCH) -> None:
+    """Dequantising int8 GEMM whose [M, N] block is stored at column `col_offset` of every destination matrix
+    [M, n_total] (row-major, contiguous) given by raw device pointers (this GPU's buffer and peers' mapped buffers)."""
+    import ctypes
+    nat.require_device(q.device)
+    q, w = _rows(q), _rows(w)
+    M, K = q.shape
+    N = w.shape[0]
+    ws, mode = _wscale_arg(w_scale, q.device)
+    if bias is not None:
+        bias = bias.to(q.device).contiguous()
+    arr = (ctypes.c_void_p * len(dest_ptrs))(*[ctypes.c_void_p(int(p)) for p in dest_ptrs])
+    nat.check(nat.load().i8f_linear_w8a8_scatter(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w),
+                                                 nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                                 arr, len(dest_ptrs), n_total, n_total, col_offset, _code(out_dtype), M, N, K,
+                                                 order, nat.current_stream(q.device)), "i8f_linear_w8a8_scatter")
+
+
 def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype, hadamard: bool = False,
                    order: int = nat.EPI_PYTORCH, workspace: Tensor | None = None) -> Tensor:
     """(rotate) -> quantise -> int8 GEMM -> dequant (+bias) through the single fused entry point."""

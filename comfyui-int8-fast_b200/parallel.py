@@ -89,3 +89,37 @@ def column_parallel_linear(x: Tensor, shard: ColumnShard, out_dtype: torch.dtype
         linear_fn = F.linear_forward
     y_local = linear_fn(x, shard.weight, shard.weight_scale, shard.bias, out_dtype, hadamard=hadamard)
     return all_gather_columns(y_local, shard.out_features, group=group)
+
+
+class FusedColumnParallelOutput:
+    """Every rank's copy of the full [M, N] activation in symmetric memory, for the fused form of the
+    column-parallel linear: the GEMM epilogue stores each finished tile of this rank's column block into all
+    ranks' copies (TMA stores to this GPU's memory and, over NVLink, to the peers' mapped buffers), so there is
+    no separate all-gather pass and the transfer overlaps the tensor-core main loop.  Only stores cross GPUs.
+
+    After `forward` returns, the local copy holds all columns once every rank's kernel has finished; `forward`
+    ends with a barrier over the symmetric-memory signal pads, stream-ordered on the current stream.
+    """
+
+    def __init__(self, rows: int, out_features: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.out_features = out_features
+        self.buffer = symm_mem.empty((rows, out_features), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # own buffer first: the local store is the cheap one
+        self.dest_ptrs = [self.peer_ptrs[self.rank]] + [p for r, p in enumerate(self.peer_ptrs) if r != self.rank]
+
+    def forward(self, x: Tensor, shard: ColumnShard, hadamard: bool = False) -> Tensor:
+        from . import functional as F
+        if (shard.end - shard.begin) % 32:
+            raise ValueError("the fused column-parallel path needs a block width that is a multiple of 32")
+        q, xs = F.quantize_rowwise(x, hadamard=hadamard)
+        self.handle.barrier(channel=0)        # nobody still reads the previous step's result
+        F.linear_w8a8_scatter(q, xs, shard.weight, shard.weight_scale, shard.bias, self.dest_ptrs, self.out_features,
+                              shard.begin, self.buffer.dtype)
+        self.handle.barrier(channel=1)        # every rank's block has landed everywhere
+        return self.buffer[: x.shape[0]]

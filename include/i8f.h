@@ -129,6 +129,19 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale,
                         void* out, int out_dtype, int64_t ldo,
                         int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
+/* Column-parallel form: computes this GPU's [M,N] block of a wider output (N = n_total / P output channels)
+ * and stores it at column `col_offset` of n_dests destination matrices [M, n_total] (pitch ld_dest), which are
+ * this GPU's and its peers' copies of the full output (peer pointers mapped into this process, e.g. CUDA IPC or
+ * symmetric memory).  The tiles leave the epilogue as TMA stores to every destination, so the all-gather of a
+ * column-parallel linear overlaps the tensor-core main loop instead of following it.  No load ever touches peer
+ * memory.  The caller orders the peers (a barrier after the kernel) before anyone reads its copy.
+ * N must be a multiple of 32; n_dests <= 8.  Has no counterpart in the reference, which is single-GPU. */
+int i8f_linear_w8a8_scatter(const int8_t* a, int64_t lda, const float* a_scale,
+                            const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                            const void* bias, int bias_dtype,
+                            void* const* dests, int n_dests, int64_t ld_dest, int64_t n_total, int64_t col_offset,
+                            int out_dtype, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
+
 /* Bytes of caller-owned workspace i8f_linear_forward needs for an [M,K] input. */
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K);
 

@@ -229,6 +229,26 @@ def test_split_calls_equal_fused_call(cuda_pkg):
     assert torch.equal(y1, y2)
 
 
+def test_scatter_epilogue_writes_every_destination(cuda_pkg):
+    """The column-parallel epilogue on one GPU: a [M, N] block goes to column `col_offset` of two destination
+    matrices (standing in for this GPU's and a peer's copy of the full output); nothing else is touched."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    M, K, N, n_total, off = 300, 512, 256, 1024, 512
+    x = wl.activation(M, K, seed=14).to(DEV)
+    wq, ws = F.quantize_weight_rows(wl.weight_fp32(N, K, seed=14).to(DEV))
+    b = wl.bias_fp32(N, seed=14).to(DEV)
+    q, s = F.quantize_rowwise(x)
+    want = F.linear_w8a8(q, s, wq, ws, b, torch.bfloat16)
+    dests = [torch.full((M, n_total), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    F.linear_w8a8_scatter(q, s, wq, ws, b, [d.data_ptr() for d in dests], n_total, off, torch.bfloat16)
+    for d in dests:
+        assert torch.equal(d[:, off:off + N], want)
+        assert bool((d[:, :off] == 7.0).all()) and bool((d[:, off + N:] == 7.0).all())
+    nat = cuda_pkg._native
+    with pytest.raises(nat.NativeLibraryError, match="multiple of 32"):
+        F.linear_w8a8_scatter(q, s, wq[:100], ws[:100], None, [dests[0].data_ptr()], n_total, 0, torch.bfloat16)
+
+
 # ------------------------------------------------------------ K3 dynamic LoRA
 @pytest.mark.parametrize("M,K,N,r,dt", [(256, 512, 384, 64, torch.bfloat16), (200, 1024, 328, 16, torch.bfloat16),
                                         (130, 256, 520, 8, torch.bfloat16), (96, 384, 160, 32, torch.float16),
