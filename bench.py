@@ -620,12 +620,123 @@ def run_column_parallel(args):
                               f"{NVLINK_PEER_GBS} GB/s per direction per GPU (measured peer copy)"}))
 
 
+# ------------------------------------------- stochastic LoRA merge (config 2, second variant)
+def run_merge(args):
+    """One step = one stochastic-rounding merge of a rank-64 LoRA (bf16 factors, Philox uniforms keyed by the
+    node's seed) into int8 weights [4096, 4096] with per-channel scales.  HBM-bound by design: the algorithmic
+    traffic is the weights read + written plus the factors and scales."""
+    import torch
+    import __graft_entry__ as g
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    N = K = 4096
+    r = 64
+    bytes_step = 2.0 * N * K + 2.0 * r * (N + K) + 4.0 * N
+    pkg = g.load_package()
+    wl = pkg.workloads
+    cfg = {"workload": "c2_stochastic_lora_merge", "N": N, "K": K, "rank": r, "factors": "bf16", "weight_scale": "per_channel",
+           "rng": "Philox4x32-10, seed 318008", "parallelism": f"independent layers x{world}",
+           "l2": "weights rotate over 8 buffers (134 MB > 126 MB L2)"}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import torch_path as tp
+        torch.set_num_threads(os.cpu_count() or 1)
+        w = wl.weight_fp32(N, K, seed=0)
+        wq, ws = tp.quantize_rowwise(w)
+        down, up = wl.lora_factors(N, K, r, seed=0)
+        u = wl.uniforms(N, K, seed=0)
+        tp.lora_merge(wq, ws, up, down, 1.0, u)
+        n = max(1, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            tp.lora_merge(wq, ws, up, down, 1.0, u)
+        dt = (time.perf_counter() - t0) / n
+        base = {"value": bytes_step / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+                "sample": f"the full merge, {n} passes of {dt * 1e3:.1f} ms (uniforms pre-drawn)"}
+        print(json.dumps({"impl": "reference", "metric": "lora_merge_sr_bandwidth", "value": base["value"], "unit": "GB/s",
+                          "n_gpus": args.gpus, "steps": n, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": cfg,
+                          "cpu_baseline": base, "gpu_launches": 0,
+                          "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    F = pkg.functional
+    wq0, ws = F.quantize_weight_rows(wl.weight_fp32(N, K, seed=rank).to(dev))
+    down, up = wl.lora_factors(N, K, r, seed=rank)
+    down, up = down.to(dev), up.to(dev)
+    bufs = [wq0.clone() for _ in range(8)]
+    for i in range(max(3, args.warmup)):
+        F.lora_merge_sr_(bufs[i % 8], ws, up, down, 1.0, seed=318008)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0 = time.perf_counter()
+    a.record()
+    for i in range(args.steps):
+        F.lora_merge_sr_(bufs[i % 8], ws, up, down, 1.0, seed=318008)
+    b.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    h1 = time.perf_counter()
+    ms = a.elapsed_time(b) / args.steps
+    clocks = sampler.stop(h0, h1) if sampler else None
+    # end to end: int8 weights and factors from pinned host memory, merged weights back to the host
+    w_host, out_host = wq0.cpu().pin_memory(), torch.empty((N, K), dtype=torch.int8).pin_memory()
+    up_h, down_h = up.cpu().pin_memory(), down.cpu().pin_memory()
+    e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        wd = w_host.to(dev, non_blocking=True)
+        F.lora_merge_sr_(wd, ws, up_h.to(dev, non_blocking=True), down_h.to(dev, non_blocking=True), 1.0, seed=318008)
+        out_host.copy_(wd, non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(e_steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    e2e_ms = a.elapsed_time(b) / e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in t.tolist())
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    peaks, kind = measured_peaks()
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "lora_merge_sr_bandwidth", "value": world * achieved, "unit": "GB/s", "n_gpus": world,
+                      "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": cfg,
+                      "roofline": {"bound": "hbm", "kernel": "lora_merge_tc_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                                   "peak_source": f"hbm_gbs of {kind} MEASURED_PEAKS.json; time includes host launch gaps "
+                                                  "(one launch per step, back to back)"},
+                      "e2e": {"value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                              "h2d_bytes_per_step": N * K + 2 * r * (N + K), "d2h_bytes_per_step": N * K, "steps": e_steps},
+                      "gpu_launches": args.steps * world, "clocks": clocks, "device_status": pkg._native.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c4", "dit"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     args = ap.parse_args()
@@ -635,6 +746,8 @@ def main():
         run_dit(args)
     elif args.workload == "c4":
         run_column_parallel(args)
+    elif args.workload == "c2merge":
+        run_merge(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
