@@ -234,18 +234,21 @@ def run_gpu_arm(args):
     def step(i: int, timed: bool):
         s = sets[i % N_BUFFER_SETS]
         q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
-        # dynamic LoRA: the low-rank term is stored first, the int8 GEMM adds onto it in its epilogue
-        lora_y = F.lora_up(F.lora_down(s["x"], s["lora"][0]), s["lora"][1]) if s["lora"] is not None else None
+        # dynamic LoRA: t = x @ A^T, then the int8 GEMM accumulates t @ B^T in a second tensor-memory accumulator
+        lora_t = F.lora_down(s["x"], s["lora"][0]) if s["lora"] is not None else None
         if timed:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype, add_into=lora_y)
+        if lora_t is not None:
+            y = F.linear_w8a8_lora(q, xs, s["wq"], s["ws"], s["bias"], lora_t, s["lora"][1], out_dtype)
+        else:
+            y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype)
         if timed:
             e1.record()
             gemm_events.append((e0, e1))
         return y
 
-    launches_per_step = 2 + (2 if shape.lora_rank else 0)
+    launches_per_step = 2 + (1 if shape.lora_rank else 0)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -280,8 +283,7 @@ def run_gpu_arm(args):
         xd = s["x_host"].to(dev, non_blocking=True)
         if s["lora"] is not None:
             q, xs = F.quantize_rowwise(xd, hadamard=shape.hadamard)
-            y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype,
-                              add_into=F.lora_up(F.lora_down(xd, s["lora"][0]), s["lora"][1]))
+            y = F.linear_w8a8_lora(q, xs, s["wq"], s["ws"], s["bias"], F.lora_down(xd, s["lora"][0]), s["lora"][1], out_dtype)
         else:
             y = F.linear_forward(xd, s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard)
         s["y_host"].copy_(y, non_blocking=True)
@@ -322,7 +324,7 @@ def run_gpu_arm(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": config_dict(shape, world),
         "frac_of_nominal_int8_peak": value / (world * NOMINAL_INT8_TOPS),
-        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8,256>", "achieved": achieved, "peak": peak_tops,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8, pair" + (", fused LoRA>" if shape.lora_rank else ">"), "achieved": achieved, "peak": peak_tops,
                      "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": None,
                      "peak_source": f"2 x bf16_tflops (burst) of {peak_kind} MEASURED_PEAKS.json; int8 ops counted as 2*M*N*K",
                      "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "kernel_ms_avg": gemm_avg_ms,

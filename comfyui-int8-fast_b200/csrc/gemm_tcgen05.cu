@@ -63,6 +63,8 @@ struct GemmParams {
     int add_existing;  // dequant mode: out = round(round(result) + out) (a LoRA term already stored in out)
     int vec_ok;  // out pointer / pitch allow 16-byte row-segment stores
     int tma_out; // 16-bit output leaves through shared memory and TMA stores (needs vec_ok)
+    int lora_k_blocks;  // fused dynamic LoRA: 64-element slabs of the rank (0 = none)
+    int lora_bf16;      // its operand type (else fp16)
     int n_out;   // number of destinations (tensor maps) every output chunk is stored to
     int out_col0; // column of the destination matrices at which this launch's block starts
     int* status;
@@ -76,14 +78,27 @@ struct alignas(64) OutMaps {
     CUtensorMap m[kMaxOutputs];
 };
 
-template <int BN, bool PAIR>
+// LORA: a second, fp32 accumulator per buffer holds t @ lora_b^T (kind::f16 MMAs issued after the int8 K loop of
+// the same tile), so the dynamic-LoRA term is added in the epilogue without ever touching global memory.
+struct alignas(64) LoraMaps {
+    CUtensorMap t;   // t [M, r], box 64 x 128 rows
+    CUtensorMap b;   // lora_b [N, r], box 64 x (rows of B per CTA)
+};
+
+template <int BN, bool PAIR, bool LORA = false>
 struct Cfg {
     static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA stages
     static constexpr int kABytes = kBM * kStageRowBytes;
     static constexpr int kBBytes = kBRows * kStageRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (192 * 1024) / kStageBytes;
-    static constexpr int kTmemCols = 2 * BN;  // 512, 256 or 128: powers of two >= 32
+    static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
+    // TMEM: two int32/fp32 accumulator buffers at columns 0 and BN; with LORA one more fp32 accumulator at 2*BN.
+    // The LoRA accumulator needs no double buffering: it is written at the very end of a tile's MMA sequence, long
+    // after the epilogue of the previous tile (which overlaps this tile's int8 K loop) has drained it.
+    static constexpr int kLoraCol = 2 * BN;
+    static constexpr int kColsUsed = LORA ? 3 * BN : 2 * BN;
+    static constexpr int kTmemCols = kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512);   // power of two >= 32
+    static_assert(kColsUsed <= 512, "tensor memory has 512 columns");
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kEpiBytes = 4 * 2 * BN * 4;  // per epilogue warp: BN column scales + BN biases (fp32)
     static constexpr int kOutStageBytes = 4 * 2 * 2048;  // per epilogue warp: two 32-row x 64-byte output chunks
@@ -221,10 +236,11 @@ __device__ __forceinline__ void old_values(const GemmParams& p, long long row, i
 // every lane reads the same address, a broadcast.  The result goes either straight to global memory or,
 // when `stage` is non-zero, into this warp's shared-memory staging chunk (row = lane, 64 bytes per row,
 // 16-byte pieces XOR-swizzled with (row >> 1) & 3 as the TMA 64-byte swizzle expects).
-template <int OUT>
+template <int OUT, bool LORA>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, bool row_ok, int col,
-                                               const uint32_t (&v)[32], float row_scale, float ws_scalar, const float* cs,
-                                               const float* cb, const OldChunk& old, uint32_t stage, int lane) {
+                                               const uint32_t (&v)[32], const uint32_t (&lv)[LORA ? 32 : 1], float row_scale,
+                                               float ws_scalar, const float* cs, const float* cb, const OldChunk& old,
+                                               uint32_t stage, int lane) {
     float y[32];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
@@ -251,6 +267,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
 #pragma unroll
                 for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], cb[j]);
             }
+        }
+        if constexpr (LORA) {
+            // y + lora_y.to(y.dtype): both terms rounded to the output type first, as the reference does
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), round_out<OUT>(__uint_as_float(lv[j])));
         }
         if (p.add_existing && row_ok) {
             float prev[32];
@@ -299,11 +320,12 @@ __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long r
     }
 }
 
-template <int KIND, int BN, bool PAIR>
+template <int KIND, int BN, bool PAIR, bool LORA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ OutMaps outs, const GemmParams p) {
-    using C = Cfg<BN, PAIR>;
+                    const __grid_constant__ OutMaps outs, const __grid_constant__ LoraMaps lora, const GemmParams p) {
+    using C = Cfg<BN, PAIR, LORA>;
+    static_assert(!LORA || (KIND == kKindI8 && PAIR), "the fused LoRA accumulator exists for the paired int8 kernel");
     constexpr int kElemsPerStage = (KIND == kKindI8) ? kStageRowBytes : kStageRowBytes / 2;
     constexpr uint32_t kIdesc = (KIND == kKindI8)     ? make_idesc(kDFmtS32, kFmtS8, C::kTileM, BN)
                                 : (KIND == kKindBF16) ? make_idesc(kDFmtF32, kFmtBF16, C::kTileM, BN)
@@ -396,6 +418,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         phase ^= 1u;
                     }
                 }
+                if constexpr (LORA) {
+                    // the low-rank operands ride the same ring: t rows where A rows go, lora_b rows where W rows go
+                    for (int lb = 0; ok && lb < p.lora_k_blocks; ++lb) {
+                        if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.status, kStEmptyWait)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t a_dst = smem_base + stage * C::kStageBytes;
+                        const uint32_t bar = mapa_cluster(full0 + 8 * stage, 0);
+                        if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * C::kStageBytes);
+                        tma_load_2d_pair(a_dst, &lora.t, bar, lb * 64, row_a);
+                        tma_load_2d_pair(a_dst + C::kABytes, &lora.b, bar, lb * 64, row_b);
+                        if (++stage == C::kStages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
             }
         }
     } else if (warp == 1) {
@@ -439,6 +479,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
                 if (!ok) break;
+                if constexpr (LORA) {
+                    const uint32_t idesc_lora = p.lora_bf16 ? make_idesc(kDFmtF32, kFmtBF16, C::kTileM, BN)
+                                                            : make_idesc(kDFmtF32, kFmtF16, C::kTileM, BN);
+                    // the (single) LoRA accumulator was last read by the epilogue of the previous tile, which owns the
+                    // other int32 buffer: its hand-back covers both.  Re-waiting a completed phase returns at once.
+                    if (t != tile_first) {
+                        const uint32_t prev_phase = (buf == 1) ? acc_phase : (acc_phase ^ 1u);
+                        if (!mbar_wait_bounded(accempty0 + 8 * (buf ^ 1), prev_phase, abort_flag, p.status, kStAccEmptyWait)) break;
+                        tc_fence_after_sync();
+                    }
+                    for (int lb = 0; lb < p.lora_k_blocks; ++lb) {
+                        if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t a_src = smem_base + stage * C::kStageBytes;
+                        const uint64_t adesc = make_smem_desc_sw128(a_src);
+                        const uint64_t bdesc = make_smem_desc_sw128(a_src + C::kABytes);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)   // 16 elements = 32 bytes of the rank per instruction
+                            mma_f16_pair(tmem_base + C::kLoraCol, adesc + 2 * k, bdesc + 2 * k, idesc_lora, (lb | k) != 0 ? 1u : 0u);
+                        mma_commit_pair(empty0 + 8 * stage);
+                        if (++stage == C::kStages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                }
                 if constexpr (PAIR) mma_commit_pair(accfull0 + 8 * buf);  // accumulator complete
                 else mma_commit(accfull0 + 8 * buf);
                 buf ^= 1;
@@ -489,12 +559,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
             tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+            const uint32_t t_lora = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(C::kLoraCol);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 const int col = n_blk * BN + c * 32;
                 if (col >= p.N) break;                      // uniform over the CTA
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + c * 32, v);
+                uint32_t lv[LORA ? 32 : 1];
+                if constexpr (LORA) tmem_ld_32x32(t_lora + c * 32, lv);
                 const OldChunk old_cur = old_next;
                 if (need_old && c + 1 < BN / 32 && col + 32 < p.N) prefetch_old(p, row, row_ok, col + 32, old_next);
                 uint32_t stage = 0;
@@ -508,11 +581,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (p.epi_mode == kEpiI32) {
                     if (row_ok) store_i32_row32(p, row, col, v);
                 } else if (p.out_dtype == I8F_BF16) {
-                    epilogue_chunk<I8F_BF16>(p, row, row_ok, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32,
-                                             old_cur, stage, lane);
+                    epilogue_chunk<I8F_BF16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
+                                                   col_bias + c * 32, old_cur, stage, lane);
                 } else {
-                    epilogue_chunk<I8F_F16>(p, row, row_ok, col, v, row_scale, ws_scalar, col_scale + c * 32, col_bias + c * 32,
-                                            old_cur, stage, lane);
+                    epilogue_chunk<I8F_F16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
+                                                  col_bias + c * 32, old_cur, stage, lane);
                 }
                 if (tma_out) {
                     fence_proxy_async_smem();               // generic-proxy writes -> visible to the TMA engine
@@ -630,11 +703,29 @@ struct Scatter {
     int64_t col_offset;
 };
 
-template <int KIND, int BN, bool PAIR>
+struct LoraOperands {
+    const void* t;        // [M, r], pitch ldt
+    int64_t ldt;
+    const void* b;        // [N, r], pitch ldb
+    int64_t ldb;
+    int64_t r;
+    int kind;             // kKindBF16 or kKindF16
+};
+
+template <int KIND, int BN, bool PAIR, bool LORA = false>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K, GemmParams p,
-                cudaStream_t st, const Scatter* scatter = nullptr) {
-    using C = Cfg<BN, PAIR>;
+                cudaStream_t st, const Scatter* scatter = nullptr, const LoraOperands* lo = nullptr) {
+    using C = Cfg<BN, PAIR, LORA>;
     CUtensorMap tmA, tmB;
+    LoraMaps lmaps{};
+    if (LORA) {
+        int rc_l = make_operand_map(&lmaps.t, lo->kind, lo->t, M, lo->r, lo->ldt, kBM);
+        if (rc_l != I8F_OK) return rc_l;
+        rc_l = make_operand_map(&lmaps.b, lo->kind, lo->b, N, lo->r, lo->ldb, C::kBRows);
+        if (rc_l != I8F_OK) return rc_l;
+        p.lora_k_blocks = static_cast<int>((lo->r + 63) / 64);
+        p.lora_bf16 = lo->kind == kKindBF16 ? 1 : 0;
+    }
     int rc = make_operand_map(&tmA, KIND, a, M, K, lda, kBM);
     if (rc != I8F_OK) return rc;
     rc = make_operand_map(&tmB, KIND, b, N, K, ldb, C::kBRows);
@@ -671,7 +762,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     p.tiles_n = static_cast<int>((N + BN - 1) / BN);
     p.status = device_status_word();
     I8F_REQUIRE(p.status != nullptr, I8F_ERR_CUDA, "device status word unavailable");
-    auto kern = gemm_tcgen05_kernel<KIND, BN, PAIR>;
+    auto kern = gemm_tcgen05_kernel<KIND, BN, PAIR, LORA>;
     static bool attr_done[64] = {false};
     static int max_clusters[64] = {0};
     const int dev = current_device();
@@ -716,7 +807,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     } else {
         cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()), 1, 1);
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, outs, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, outs, lmaps, p);
     if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "gemm_tcgen05_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tcgen05_kernel");
 }
@@ -815,6 +906,59 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale, cons
                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
     return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
                             epilogue_order, 1, stream);
+}
+
+int i8f_linear_w8a8_lora(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                         const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, const void* t, int64_t ldt,
+                         const void* lora_b, int64_t ldb, int64_t r, void* out, int out_dtype, int64_t ldo, int64_t M,
+                         int64_t N, int64_t K, int epilogue_order, void* stream) {
+    I8F_REQUIRE(out_dtype == I8F_BF16 || out_dtype == I8F_F16, I8F_ERR_UNSUPPORTED, "out_dtype must be bf16 or f16");
+    if (r <= 0)
+        return i8f_linear_w8a8(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
+                               epilogue_order, stream);
+    I8F_REQUIRE(t != nullptr && lora_b != nullptr && ldt >= r && ldb >= r, I8F_ERR_INVALID_ARG, "bad low-rank operands");
+    static const int no_fuse = [] {
+        const char* e = getenv("I8F_LORA_UNFUSED");
+        return (e != nullptr && e[0] == '1') ? 1 : 0;
+    }();
+    const bool fused = M > 128 && N > 128 && !no_fuse;
+    if (!fused) {
+        // small shapes: the low-rank term is stored first, the int8 GEMM adds onto it in its epilogue
+        int rc0 = i8f_lora_up(t, ldt, lora_b, ldb, out, ldo, out_dtype, M, N, r, stream);
+        if (rc0 != I8F_OK) return rc0;
+        return i8f_linear_w8a8_add(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N,
+                                   K, epilogue_order, stream);
+    }
+    int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
+    if (rc != I8F_OK) return rc;
+    rc = check_operands(t, ldt, lora_b, ldb, 2, M, N, r);
+    if (rc != I8F_OK) return rc;
+    I8F_REQUIRE(a_scale != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL scale pointer");
+    I8F_REQUIRE(w_scale_mode == I8F_WSCALE_TENSOR || w_scale_mode == I8F_WSCALE_CHANNEL, I8F_ERR_INVALID_ARG,
+                "unknown w_scale_mode %d", w_scale_mode);
+    I8F_REQUIRE(out != nullptr && ldo >= N, I8F_ERR_INVALID_ARG, "bad output");
+    I8F_REQUIRE(bias == nullptr || dtype_size(bias_dtype) != 0, I8F_ERR_INVALID_ARG, "unknown bias dtype %d", bias_dtype);
+    I8F_REQUIRE(epilogue_order == I8F_EPI_PYTORCH || epilogue_order == I8F_EPI_SINGLE, I8F_ERR_INVALID_ARG,
+                "unknown epilogue_order %d", epilogue_order);
+    GemmParams p{};
+    p.out = out;
+    p.ldo = ldo;
+    p.out_dtype = out_dtype;
+    p.a_scale = a_scale;
+    p.w_scale = w_scale;
+    p.w_scale_mode = w_scale_mode;
+    p.bias = bias;
+    p.bias_dtype = bias_dtype;
+    p.epi_mode = kEpiDequant;
+    p.epi_order = epilogue_order;
+    p.vec_ok = aligned16(out) && (ldo % 8 == 0);
+    const LoraOperands lo{t, ldt, lora_b, ldb, r, out_dtype == I8F_BF16 ? kKindBF16 : kKindF16};
+    static const int bn160 = [] {
+        const char* e = getenv("I8F_LORA_BN");
+        return (e != nullptr && e[0] == '1' && e[1] == '2') ? 0 : 1;   // I8F_LORA_BN=128 selects the narrower tile
+    }();
+    if (bn160) return launch_gemm<kKindI8, 160, true, true>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), nullptr, &lo);
+    return launch_gemm<kKindI8, 128, true, true>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), nullptr, &lo);
 }
 
 int i8f_linear_w8a8_scatter(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,

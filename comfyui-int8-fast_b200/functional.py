@@ -139,6 +139,28 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
     return out
 
 
+def linear_w8a8_lora(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, t: Tensor, lora_b: Tensor,
+                     out_dtype: torch.dtype, order: int = nat.EPI_PYTORCH) -> Tensor:
+    """Dequantising int8 GEMM with the dynamic-LoRA term round(t @ lora_b^T) added inside the kernel."""
+    nat.require_device(q.device)
+    q, w = _rows(q), _rows(w)
+    t, lora_b = _rows(t.to(out_dtype)), _rows(lora_b.to(out_dtype))
+    M, K = q.shape
+    N = w.shape[0]
+    r = t.shape[1]
+    ws, mode = _wscale_arg(w_scale, q.device)
+    if bias is not None:
+        bias = bias.to(q.device).contiguous()
+    out = torch.empty((M, N), dtype=out_dtype, device=q.device)
+    if M and N:
+        nat.check(nat.load().i8f_linear_w8a8_lora(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w),
+                                                  nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                                  nat.ptr(t), _ld(t), nat.ptr(lora_b), _ld(lora_b), r, nat.ptr(out),
+                                                  _code(out_dtype), N, M, N, K, order, nat.current_stream(q.device)),
+                  "i8f_linear_w8a8_lora")
+    return out
+
+
 def linear_w8a8_scatter(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, dest_ptrs: list[int],
                         n_total: int, col_offset: int, out_dtype: torch.dtype, order: int = nat.EPI_PYTORCH) -> None:
     """Dequantising int8 GEMM whose [M, N] block is stored at column `col_offset` of every destination matrix

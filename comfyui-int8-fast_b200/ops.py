@@ -539,15 +539,15 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
 
                 with torch.cuda.device(x.device):
                     if rows > SMALL_BATCH_ROWS and has_lora:
-                        # low-rank term first (stored rounded, as the reference's lora_y), then the int8 GEMM adds
-                        # onto it in its epilogue: y = round(round(dequant + bias) + lora_y)
+                        # t = x @ A^T first; t @ B^T is accumulated inside the int8 GEMM kernel and added in its
+                        # epilogue with the reference's roundings: y = round(round(dequant + bias) + round(lora_y))
                         if self._use_quarot and Int8TensorwiseOps.lora_uses_rotated_input:
                             q, qs, lora_in = F.quantize_rowwise(x2, hadamard=True, return_rotated=True)
                         else:
                             q, qs = F.quantize_rowwise(x2, hadamard=self._use_quarot)
                         lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
-                        lora_y = F.lora_up(F.lora_down(lora_in, lora_a), lora_b)
-                        y = F.linear_w8a8(q, qs, weight, w_scale, bias, compute_dtype, add_into=lora_y)
+                        y = F.linear_w8a8_lora(q, qs, weight, w_scale, bias, F.lora_down(lora_in, lora_a), lora_b,
+                                               compute_dtype)
                     elif rows > SMALL_BATCH_ROWS:
                         y = F.linear_forward(x2, weight, w_scale, bias, compute_dtype, hadamard=self._use_quarot,
                                              workspace=self._workspace_for(rows, x.device))

@@ -129,6 +129,19 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale,
                         void* out, int out_dtype, int64_t ldo,
                         int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
+/* Quantised linear with the dynamic-LoRA term fused in:
+ *   out = round(round(dequant (+bias)) + round(t [M,r] @ lora_b [N,r]^T))
+ * t and lora_b are in out_dtype (bf16 or fp16), pitches multiples of 8 elements.  The low-rank product is
+ * accumulated by the tensor cores in a second (fp32) tensor-memory accumulator next to the int32 one, from
+ * operands that ride the same TMA ring as the int8 tiles; the sum never goes through global memory.
+ * Replaces the dequant epilogue plus int8_quant.py:769-774 (t comes from i8f_lora_down, :768). */
+int i8f_linear_w8a8_lora(const int8_t* a, int64_t lda, const float* a_scale,
+                         const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                         const void* bias, int bias_dtype,
+                         const void* t, int64_t ldt, const void* lora_b, int64_t ldb, int64_t r,
+                         void* out, int out_dtype, int64_t ldo,
+                         int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
+
 /* Column-parallel form: computes this GPU's [M,N] block of a wider output (N = n_total / P output channels)
  * and stores it at column `col_offset` of n_dests destination matrices [M, n_total] (pitch ld_dest), which are
  * this GPU's and its peers' copies of the full output (peer pointers mapped into this process, e.g. CUDA IPC or

@@ -291,6 +291,31 @@ def test_lora_term_added_in_the_gemm_epilogue(cuda_pkg):
     y_rmw = F.linear_w8a8(q, s, torch.from_numpy(wq).to(DEV), dev_ws(ws), b.to(DEV), torch.bfloat16)
     F.lora_up_add_(y_rmw, t, B.to(DEV))
     assert torch.equal(y_rmw, y)                            # same result as the read-modify-write form
+    # fully fused: t @ B^T accumulated in tensor memory next to the int32 accumulator
+    y_fused = F.linear_w8a8_lora(q, s, torch.from_numpy(wq).to(DEV), dev_ws(ws), b.to(DEV), t, B.to(DEV), torch.bfloat16)
+    assert np.max(np.abs(to_np(y_fused) - want)) <= TOL * rms(want)
+    assert (to_np(y_fused) != want).mean() <= 1e-2          # fp32 accumulation order of the low-rank product only
+
+
+@pytest.mark.parametrize("M,K,N,r,per_ch,dt", [(520, 384, 392, 64, True, torch.bfloat16), (4608, 512, 1024, 16, False, torch.bfloat16),
+                                               (300, 256, 264, 136, True, torch.float16), (100, 256, 264, 8, True, torch.bfloat16),
+                                               (300, 256, 96, 8, False, torch.bfloat16)])
+def test_fused_lora_linear_matches_oracle(cuda_pkg, M, K, N, r, per_ch, dt):
+    """i8f_linear_w8a8_lora (fused for M, N > 128, two-kernel form below that) against the oracle."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=15, dtype=dt)
+    w = wl.weight_fp32(N, K, seed=15).numpy()
+    wq, ws = bs.quantize_rowwise(w) if per_ch else bs.quantize_tensorwise(w)
+    b = wl.bias_fp32(N, seed=15).to(dt)
+    A, B = wl.lora_factors(N, K, r, seed=15, dtype=dt)
+    xd = x.to(DEV)
+    q, s = F.quantize_rowwise(xd)
+    t = F.lora_down(xd, A.to(DEV))
+    y = F.linear_w8a8_lora(q, s, torch.from_numpy(wq).to(DEV), dev_ws(ws), b.to(DEV), t, B.to(DEV), dt)
+    base = bs.linear_w8a8(to_np(x), wq, ws, to_np(b), act_dtype=NAME[dt])
+    want = bs.lora_up_add(base, to_np(t), to_np(B), NAME[dt])
+    assert np.max(np.abs(to_np(y) - want)) <= TOL * rms(want)
+    assert (to_np(y) != want).mean() <= 2e-2
 
 
 def test_module_golden_with_dynamic_lora(cuda_pkg, golden):
