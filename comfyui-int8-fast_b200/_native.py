@@ -32,6 +32,7 @@ _PROTOTYPES = {
     "i8f_last_error": (c_char_p, []),
     "i8f_device_check": (c_int, []),
     "i8f_device_status": (c_int, [ctypes.POINTER(c_int), c_int]),
+    "i8f_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "i8f_quant_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                   c_void_p, c_void_p]),
     "i8f_quant_tensorwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,

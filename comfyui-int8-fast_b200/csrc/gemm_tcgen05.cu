@@ -65,6 +65,7 @@ struct GemmParams {
     int tma_out; // 16-bit output leaves through shared memory and TMA stores (needs vec_ok)
     int lora_k_blocks;  // fused dynamic LoRA: 64-element slabs of the rank (0 = none)
     int lora_bf16;      // its operand type (else fp16)
+    int wide_out;       // scatter mode: 64-column (128-byte) store boxes
     int n_out;   // number of destinations (tensor maps) every output chunk is stored to
     int out_col0; // column of the destination matrices at which this launch's block starts
     int* status;
@@ -240,7 +241,7 @@ template <int OUT, bool LORA>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, bool row_ok, int col,
                                                const uint32_t (&v)[32], const uint32_t (&lv)[LORA ? 32 : 1], float row_scale,
                                                float ws_scalar, const float* cs, const float* cb, const OldChunk& old,
-                                               uint32_t stage, int lane) {
+                                               uint32_t stage, int lane, int wide_half = -1) {
     float y[32];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
@@ -292,11 +293,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
         for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], round_out<OUT>(__uint_as_float(v[j])));
     }
     if (stage != 0) {
-        const uint32_t row_addr = stage + static_cast<uint32_t>(lane) * 64u;
-        const uint32_t x = static_cast<uint32_t>(lane >> 1) & 3u;
+        // narrow: 64-byte rows, 64-byte swizzle; wide (wide_half 0/1): this chunk is one half of a 128-byte row,
+        // 128-byte swizzle (16-byte piece index XOR row & 7)
+        const bool wide = wide_half >= 0;
+        const uint32_t row_addr = stage + static_cast<uint32_t>(lane) * (wide ? 128u : 64u);
+        const uint32_t x = wide ? (static_cast<uint32_t>(lane) & 7u) : (static_cast<uint32_t>(lane >> 1) & 3u);
+        const uint32_t g0 = wide ? static_cast<uint32_t>(wide_half) * 4u : 0u;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const uint32_t a = row_addr + ((static_cast<uint32_t>(g) ^ x) << 4);
+            const uint32_t a = row_addr + (((g0 + static_cast<uint32_t>(g)) ^ x) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<OUT>(y[8 * g + 0], y[8 * g + 1])),
                          "r"(pack2<OUT>(y[8 * g + 2], y[8 * g + 3])), "r"(pack2<OUT>(y[8 * g + 4], y[8 * g + 5])),
                          "r"(pack2<OUT>(y[8 * g + 6], y[8 * g + 7]))
@@ -528,6 +533,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t accempty_leader = PAIR ? mapa_cluster(accempty0, 0) : accempty0;
         const bool need_old = (dequant && p.add_existing) || p.epi_mode == kEpiAccum;
         const bool tma_out = p.tma_out != 0;
+        const bool wide_out = p.wide_out != 0;   // implies tma_out; N is a multiple of 64
         const uint32_t out_stage = out_stage0 + static_cast<uint32_t>(warp - 2) * 4096u;
         uint32_t out_chunk = 0;
         for (int t = tile_first; t < num_tiles; t += tile_step) {
@@ -571,7 +577,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const OldChunk old_cur = old_next;
                 if (need_old && c + 1 < BN / 32 && col + 32 < p.N) prefetch_old(p, row, row_ok, col + 32, old_next);
                 uint32_t stage = 0;
-                if (tma_out) {
+                const int wide_half = wide_out ? (c & 1) : -1;
+                if (wide_out) {
+                    // scatter mode: one 4 KB buffer per warp holds 32 rows x 128 bytes (two chunks); the stores of the
+                    // previous pair of chunks must have read it before it is rewritten
+                    stage = out_stage;
+                    if (wide_half == 0) {
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+                    }
+                } else if (tma_out) {
                     stage = out_stage + static_cast<uint32_t>(out_chunk & 1) * 2048u;
                     // the store that last read this staging chunk (two chunks ago) must be done with it
                     if (lane == 0) tma_store_wait_read<1>();
@@ -582,12 +597,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (row_ok) store_i32_row32(p, row, col, v);
                 } else if (p.out_dtype == I8F_BF16) {
                     epilogue_chunk<I8F_BF16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                   col_bias + c * 32, old_cur, stage, lane);
+                                                   col_bias + c * 32, old_cur, stage, lane, wide_half);
                 } else {
                     epilogue_chunk<I8F_F16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                  col_bias + c * 32, old_cur, stage, lane);
+                                                  col_bias + c * 32, old_cur, stage, lane, wide_half);
                 }
-                if (tma_out) {
+                if (wide_out) {
+                    if (wide_half == 1) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            for (int d = 0; d < p.n_out; ++d)   // 128-byte row segments: full-size NVLink writes
+                                tma_store_2d(&outs.m[d], stage, p.out_col0 + col - 32, static_cast<int>(warp_row0));
+                            tma_store_commit();
+                        }
+                    }
+                } else if (tma_out) {
                     fence_proxy_async_smem();               // generic-proxy writes -> visible to the TMA engine
                     __syncwarp();
                     if (lane == 0) {
@@ -630,6 +655,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
+// Self-test of the bounded wait: one CTA waits on a barrier that nothing ever signals.  The wait must give up
+// after `limit_cycles`, record kStSelfTest in the status word and let the kernel end normally.
+enum : int { kStSelfTest = 199 };
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    // thread 0 hits the limit; the others see the abort flag it raises and give up as well
+    mbar_wait_bounded(smem_u32(&bar), 0u, &abort_flag, status, kStSelfTest, threadIdx.x == 0 ? limit_cycles : 4 * limit_cycles);
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------ host
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -668,15 +710,16 @@ int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, 
 }
 
 // Output [rows, cols] of 16-bit elements, box = 32 columns x 32 rows (one epilogue warp's chunk), 64-byte swizzle.
-int make_out_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld_elems) {
+int make_out_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, bool wide = false) {
     EncodeFn enc = get_encode_fn();
     I8F_REQUIRE(enc != nullptr, I8F_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems) * 2};
-    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                           CU_TENSOR_MAP_L2_PROMOTION_NONE,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     I8F_REQUIRE(r == CUDA_SUCCESS, I8F_ERR_CUDA, "cuTensorMapEncodeTiled(out) failed with CUresult %d", static_cast<int>(r));
     return I8F_OK;
@@ -738,10 +781,11 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     if (scatter != nullptr) {
         // one map per destination over the whole [M, n_total] matrix; the block lands at column out_col0
         p.tma_out = 1;
+        p.wide_out = (N % 64 == 0) ? 1 : 0;
         p.n_out = scatter->n_dests;
         p.out_col0 = static_cast<int>(scatter->col_offset);
         for (int d = 0; d < scatter->n_dests; ++d) {
-            rc = make_out_map(&outs.m[d], scatter->dests[d], M, scatter->n_total, scatter->ld);
+            rc = make_out_map(&outs.m[d], scatter->dests[d], M, scatter->n_total, scatter->ld, p.wide_out != 0);
             if (rc != I8F_OK) return rc;
         }
     } else {
@@ -850,6 +894,14 @@ int check_operands(const void* a, int64_t lda, const void* b, int64_t ldb, int e
 using namespace i8f;
 
 extern "C" {
+
+int i8f_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+    I8F_REQUIRE(limit_cycles > 0 && limit_cycles <= 4000000000LL, I8F_ERR_INVALID_ARG, "limit_cycles out of range");
+    int* status = device_status_word();
+    I8F_REQUIRE(status != nullptr, I8F_ERR_CUDA, "device status word unavailable");
+    bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_cycles);
+    return check_launch("bounded_wait_selftest_kernel");
+}
 
 int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, int32_t* acc, int64_t ldacc, int64_t M,
                     int64_t N, int64_t K, void* stream) {

@@ -48,14 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr long long kWaitLimitCycles = 2000000000LL;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* status, int code) {
+                                                  int* status, int code, long long limit_cycles = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;

@@ -69,6 +69,12 @@ int i8f_device_check(void);
  * Synchronises the device; meant for tests and diagnostics. */
 int i8f_device_status(int* status_out, int reset);
 
+/* Diagnostic: launches one CTA that waits on a barrier nothing signals.  The device-side wait gives up after
+ * `limit_cycles` SM clocks, the kernel ends normally and i8f_device_status() then reads 199.  This is how the
+ * time-out path of every in-kernel wait is exercised without hanging or faulting the GPU.  No counterpart in
+ * the reference. */
+int i8f_selftest_bounded_wait(int64_t limit_cycles, void* stream);
+
 /* Per-token absmax quantisation, optionally fused with the 128-block
  * Walsh-Hadamard rotation.
  *   x [M,K] (x_dtype) -> q int8 [M,K], scale fp32 [M]

@@ -229,11 +229,12 @@ def test_split_calls_equal_fused_call(cuda_pkg):
     assert torch.equal(y1, y2)
 
 
-def test_scatter_epilogue_writes_every_destination(cuda_pkg):
+@pytest.mark.parametrize("N", [256, 96])     # 128-byte and 64-byte store boxes
+def test_scatter_epilogue_writes_every_destination(cuda_pkg, N):
     """The column-parallel epilogue on one GPU: a [M, N] block goes to column `col_offset` of two destination
     matrices (standing in for this GPU's and a peer's copy of the full output); nothing else is touched."""
     F, wl = cuda_pkg.functional, cuda_pkg.workloads
-    M, K, N, n_total, off = 300, 512, 256, 1024, 512
+    M, K, n_total, off = 300, 512, 1024, 512
     x = wl.activation(M, K, seed=14).to(DEV)
     wq, ws = F.quantize_weight_rows(wl.weight_fp32(N, K, seed=14).to(DEV))
     b = wl.bias_fp32(N, seed=14).to(DEV)
@@ -246,7 +247,7 @@ def test_scatter_epilogue_writes_every_destination(cuda_pkg):
         assert bool((d[:, :off] == 7.0).all()) and bool((d[:, off + N:] == 7.0).all())
     nat = cuda_pkg._native
     with pytest.raises(nat.NativeLibraryError, match="multiple of 32"):
-        F.linear_w8a8_scatter(q, s, wq[:100], ws[:100], None, [dests[0].data_ptr()], n_total, 0, torch.bfloat16)
+        F.linear_w8a8_scatter(q, s, wq[:72], ws[:72], None, [dests[0].data_ptr()], n_total, 0, torch.bfloat16)
 
 
 # ------------------------------------------------------------ K3 dynamic LoRA
@@ -410,3 +411,17 @@ def test_merge_idempotent_shape_properties_at_full_size(cuda_pkg):
     assert not torch.equal(w, w0)
     F.lora_merge_sr_(w, ws, up, down, -1.0, seed=7)
     assert int((w.int() - w0.int()).abs().max()) <= 1
+
+
+def test_bounded_wait_times_out_and_reports(cuda_pkg):
+    """A device-side wait that can never be satisfied gives up after its limit, the kernel returns, the status word
+    carries the code, and the context stays usable."""
+    nat = cuda_pkg._native
+    assert nat.device_status() == 0
+    nat.check(nat.load().i8f_selftest_bounded_wait(20_000_000, nat.current_stream(torch.device(DEV))), "selftest")
+    torch.cuda.synchronize()
+    assert nat.device_status(reset=True) == 199
+    assert nat.device_status() == 0
+    got = cuda_pkg.functional.gemm_i8_i32(torch.ones(32, 64, dtype=torch.int8, device=DEV),
+                                          torch.ones(16, 64, dtype=torch.int8, device=DEV))
+    assert bool((got == 64).all())
