@@ -11,7 +11,7 @@ import logging
 
 import torch
 
-from . import _native, functional, parallel, quarot, workloads  # noqa: F401
+from . import _native, custom_ops, functional, parallel, quarot, workloads  # noqa: F401
 
 
 def _register_layouts():
@@ -20,7 +20,11 @@ def _register_layouts():
     try:
         from comfy.quant_ops import QUANT_ALGOS, QuantizedLayout, register_layout_class
     except ImportError:
-        logging.warning("INT8 Fast: ComfyUI Quantization system not found (Update ComfyUI?)")
+        try:
+            import comfy  # noqa: F401
+            logging.warning("INT8 Fast: ComfyUI Quantization system not found (Update ComfyUI?)")
+        except ImportError:
+            logging.info("INT8 Fast: running outside ComfyUI, no layout registered")
         return None
     try:
         class Int8TensorwiseLayout(QuantizedLayout):
@@ -61,7 +65,9 @@ from .ops import Int8TensorwiseOps  # noqa: E402,F401
 try:
     from .nodes import NODE_CLASS_MAPPINGS, NODE_DISPLAY_NAME_MAPPINGS
 except ImportError as e:
-    logging.error(f"INT8 Fast: Failed to import nodes: {e}")
+    # outside ComfyUI (benchmarks, tests of the kernels) there is nothing to register; inside it this is an error
+    _outside_comfy = getattr(e, "name", None) in ("comfy", "folder_paths")
+    logging.log(logging.INFO if _outside_comfy else logging.ERROR, f"INT8 Fast: Failed to import nodes: {e}")
     NODE_CLASS_MAPPINGS = {}
     NODE_DISPLAY_NAME_MAPPINGS = {}
 

@@ -385,6 +385,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch) may run while the
+    // kernel before this one in the stream is still finishing; nothing below may start before its results are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -837,20 +840,32 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute at{};
+    static const int use_pdl = [] {
+        const char* e = getenv("I8F_PDL");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    cudaLaunchAttribute at[2]{};
+    int n_at = 0;
     if (PAIR) {
         I8F_REQUIRE(max_clusters[dev] > 0, I8F_ERR_CUDA, "no CTA pair fits on this device");
         const long long clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-        at.id = cudaLaunchAttributeClusterDimension;
-        at.val.clusterDim.x = 2;
-        at.val.clusterDim.y = 1;
-        at.val.clusterDim.z = 1;
-        cfg.attrs = &at;
-        cfg.numAttrs = 1;
+        at[n_at].id = cudaLaunchAttributeClusterDimension;
+        at[n_at].val.clusterDim.x = 2;
+        at[n_at].val.clusterDim.y = 1;
+        at[n_at].val.clusterDim.z = 1;
+        ++n_at;
     } else {
         cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()), 1, 1);
     }
+    if (use_pdl) {
+        // let this kernel's set-up overlap the tail of the kernel before it (the activation quantiser)
+        at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n_at].val.programmaticStreamSerializationAllowed = 1;
+        ++n_at;
+    }
+    cfg.attrs = n_at ? at : nullptr;
+    cfg.numAttrs = n_at;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, outs, lmaps, p);
     if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "gemm_tcgen05_kernel launch: %s", cudaGetErrorString(e));
     return check_launch("gemm_tcgen05_kernel");

@@ -132,6 +132,9 @@ __global__ void __launch_bounds__(kThreads)
 quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, int8_t* __restrict__ q, int64_t ldq,
                   float* __restrict__ scale, void* __restrict__ xrot, float* __restrict__ gmax, int tpr_log2) {
     __shared__ float s_part[kThreads / 32];
+    // a GEMM launched behind this kernel with programmatic serialization may begin its set-up once every CTA of
+    // this grid has started; it still waits for this grid to complete before it reads anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int tpr = 1 << tpr_log2;
     const int rows_per_cta = kThreads >> tpr_log2;
     const int t = threadIdx.x & (tpr - 1);

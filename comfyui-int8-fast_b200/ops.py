@@ -14,6 +14,7 @@ import torch.nn.functional as TF
 from torch import Tensor, nn
 
 from . import _native as nat
+from . import custom_ops
 from . import functional as F
 from . import quarot
 
@@ -391,7 +392,6 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 self.lora_B = None
                 self.lora_alpha = None
                 self._scalar_scale_dev = None
-                self._workspace = None
 
             def reset_parameters(self):
                 return None
@@ -505,13 +505,6 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 ws = self.weight_scale
                 return ws if ws.device == device else ws.to(device, non_blocking=True)
 
-            def _workspace_for(self, rows, device):
-                need = nat.load().i8f_linear_workspace_bytes(rows, self.in_features)
-                ws = self._workspace
-                if ws is None or ws.device != device or ws.numel() < need:
-                    ws = self._workspace = torch.empty((need,), dtype=torch.uint8, device=device)
-                return ws
-
             def forward(self, x: Tensor) -> Tensor:
                 need_cast = self.comfy_cast_weights or len(self.weight_function) > 0 or len(self.bias_function) > 0
                 if not self._is_quantized:
@@ -541,16 +534,13 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     if rows > SMALL_BATCH_ROWS and has_lora:
                         # t = x @ A^T first; t @ B^T is accumulated inside the int8 GEMM kernel and added in its
                         # epilogue with the reference's roundings: y = round(round(dequant + bias) + round(lora_y))
-                        if self._use_quarot and Int8TensorwiseOps.lora_uses_rotated_input:
-                            q, qs, lora_in = F.quantize_rowwise(x2, hadamard=True, return_rotated=True)
-                        else:
-                            q, qs = F.quantize_rowwise(x2, hadamard=self._use_quarot)
                         lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
-                        y = F.linear_w8a8_lora(q, qs, weight, w_scale, bias, F.lora_down(lora_in, lora_a), lora_b,
-                                               compute_dtype)
+                        y = custom_ops.linear_lora_forward(x2, weight, w_scale, bias, lora_a, lora_b, compute_dtype,
+                                                           self._use_quarot, Int8TensorwiseOps.lora_uses_rotated_input,
+                                                           nat.EPI_PYTORCH)
                     elif rows > SMALL_BATCH_ROWS:
-                        y = F.linear_forward(x2, weight, w_scale, bias, compute_dtype, hadamard=self._use_quarot,
-                                             workspace=self._workspace_for(rows, x.device))
+                        y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
+                                                      nat.EPI_PYTORCH)
                     else:
                         if self._use_quarot:
                             lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)

@@ -234,3 +234,24 @@ def test_synthetic_dit_step_small(cuda_pkg):
     assert len(seen) == cfg.double_blocks * 8 + cfg.single_blocks * 2
     assert torch.equal(model(img, txt, t), y1)
     assert sum(p.numel() for m in model.modules() if isinstance(m, ops_cls.Linear) for p in [m.weight]) == cfg.int8_params()
+
+
+def test_linear_traces_under_torch_compile(cuda_pkg, ops):
+    """Linear.forward goes through the registered custom operators, so a compiled caller (eager backend: no code is
+    generated, only the capture is exercised) gives the same bits as the plain call."""
+    wl = cuda_pkg.workloads
+    K, N = 256, 136
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(N, K, seed=21).numpy())
+    lin = make_linear(ops, {"weight": torch.from_numpy(wq), "weight_scale": torch.from_numpy(ws),
+                            "bias": wl.bias_fp32(N, seed=21).bfloat16()}, K, N)
+    x = wl.activation(48, K, seed=21).to(DEV)
+    want = lin(x)
+    import torch._dynamo
+    torch._dynamo.reset()
+    compiled = torch.compile(lin, backend="eager")
+    assert torch.equal(compiled(x), want)
+    a, b = wl.lora_factors(N, K, 8, seed=21)
+    lin.lora_A, lin.lora_B = a.to(DEV), b.to(DEV)
+    want = lin(x)
+    torch._dynamo.reset()
+    assert torch.equal(torch.compile(lin, backend="eager")(x), want)

@@ -300,3 +300,19 @@ def test_build_hadamard_matches_sylvester(pkg):
     assert h[0, 0] > 0 and torch.allclose(h[1, :4] * (128 ** 0.5), torch.tensor([1.0, -1.0, 1.0, -1.0]))
     with pytest.raises(ValueError):
         pkg.quarot.build_hadamard(96)
+
+
+def test_custom_ops_have_shape_functions(pkg):
+    """The registered operators carry fake kernels, so tracing sees one node with a known output shape."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    assert pkg.custom_ops.linear_forward is not None
+    with FakeTensorMode():
+        x = torch.empty(40, 64, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(24, 64, dtype=torch.int8, device="cuda")
+        ws = torch.empty(24, dtype=torch.float32, device="cuda")
+        y = torch.ops.int8_fast_b200.linear_forward(x, w, ws, None, torch.bfloat16, True, 0)
+        assert y.shape == (40, 24) and y.dtype == torch.bfloat16 and y.device.type == "cuda"
+        a = torch.empty(8, 64, dtype=torch.bfloat16, device="cuda")
+        b = torch.empty(24, 8, dtype=torch.bfloat16, device="cuda")
+        y2 = torch.ops.int8_fast_b200.linear_lora_forward(x, w, ws, None, a, b, torch.float16, False, True, 0)
+        assert y2.shape == (40, 24) and y2.dtype == torch.float16
