@@ -112,6 +112,7 @@ def check(rc: int, what: str) -> None:
         raise NativeLibraryError(f"{what} failed with code {rc}: {last_error()}")
 
 
+@torch.compiler.disable
 def require_device(device: torch.device) -> None:
     """Hard requirement: a CUDA device of compute capability 10.0."""
     if device.type != "cuda":

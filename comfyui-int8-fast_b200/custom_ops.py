@@ -24,7 +24,8 @@ NAMESPACE = "int8_fast_b200"
 def _impl_linear_forward(x: Tensor, w: Tensor, w_scale: Tensor, bias: Optional[Tensor], out_dtype: torch.dtype,
                    hadamard: bool, order: int) -> Tensor:
     """[M,K] activations -> [M,N]: (rotate) -> per-token int8 -> int8 GEMM -> dequant (+bias)."""
-    return F.linear_forward(x, w, w_scale, bias, out_dtype, hadamard=hadamard, order=order)
+    with torch.cuda.device(x.device):      # the C ABI launches on the current device
+        return F.linear_forward(x, w, w_scale, bias, out_dtype, hadamard=hadamard, order=order)
 
 
 def _fake_linear_forward(x, w, w_scale, bias, out_dtype, hadamard, order):
@@ -35,12 +36,13 @@ def _impl_linear_lora_forward(x: Tensor, w: Tensor, w_scale: Tensor, bias: Optio
                         out_dtype: torch.dtype, hadamard: bool, rotated_lora_input: bool, order: int) -> Tensor:
     """The same with a dynamic LoRA: t = x_lora @ lora_a^T, then the int8 GEMM with t @ lora_b^T fused in.
     `rotated_lora_input` feeds the rotated activations to the LoRA (the reference's behaviour when QuaRot is on)."""
-    if hadamard and rotated_lora_input:
-        q, qs, lora_in = F.quantize_rowwise(x, hadamard=True, return_rotated=True)
-    else:
-        q, qs = F.quantize_rowwise(x, hadamard=hadamard)
-        lora_in = x
-    return F.linear_w8a8_lora(q, qs, w, w_scale, bias, F.lora_down(lora_in, lora_a), lora_b, out_dtype, order=order)
+    with torch.cuda.device(x.device):
+        if hadamard and rotated_lora_input:
+            q, qs, lora_in = F.quantize_rowwise(x, hadamard=True, return_rotated=True)
+        else:
+            q, qs = F.quantize_rowwise(x, hadamard=hadamard)
+            lora_in = x
+        return F.linear_w8a8_lora(q, qs, w, w_scale, bias, F.lora_down(lora_in, lora_a), lora_b, out_dtype, order=order)
 
 
 def _fake_linear_lora_forward(x, w, w_scale, bias, lora_a, lora_b, out_dtype, hadamard, rotated_lora_input, order):

@@ -349,6 +349,7 @@ class DynamicLoRAHook:
 # =============================================================================
 # Int8TensorwiseOps                                          int8_quant.py:522-792
 # =============================================================================
+@torch.compiler.disable
 def _prepare_lora(module, device: torch.device, dtype: torch.dtype):
     """lora_A / lora_B in the compute dtype on `device`, rank padded to a multiple of 8 (16-byte rows
     for the TMA loads); cached on the module until the tensors are replaced."""
@@ -495,6 +496,7 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 self._store("bias", out_bias, inplace_update)
 
             # ------------------------------------------------------------ forward
+            @torch.compiler.disable
             def _scale_on(self, device):
                 if self._weight_scale_scalar is not None:
                     cached = self._scalar_scale_dev   # (value, device, 1-element fp32 tensor)
@@ -504,6 +506,19 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     return cached[2]
                 ws = self.weight_scale
                 return ws if ws.device == device else ws.to(device, non_blocking=True)
+
+            @torch.compiler.disable
+            def _small_batch_forward(self, x2, weight, w_scale, bias, lora_in, has_lora, compute_dtype):
+                """M <= 16 tokens: dequantised weights and a plain matmul, as the reference does (int8_quant.py:756-760)."""
+                with torch.cuda.device(x2.device):
+                    if self._use_quarot:
+                        lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)
+                    w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
+                    y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
+                    if has_lora:
+                        lora_a, lora_b = _prepare_lora(self, x2.device, compute_dtype)
+                        F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)
+                return y
 
             def forward(self, x: Tensor) -> Tensor:
                 need_cast = self.comfy_cast_weights or len(self.weight_function) > 0 or len(self.bias_function) > 0
@@ -530,25 +545,18 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 has_lora = self.lora_A is not None and self.lora_B is not None
                 lora_in = x2
 
-                with torch.cuda.device(x.device):
-                    if rows > SMALL_BATCH_ROWS and has_lora:
-                        # t = x @ A^T first; t @ B^T is accumulated inside the int8 GEMM kernel and added in its
-                        # epilogue with the reference's roundings: y = round(round(dequant + bias) + round(lora_y))
-                        lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
-                        y = custom_ops.linear_lora_forward(x2, weight, w_scale, bias, lora_a, lora_b, compute_dtype,
-                                                           self._use_quarot, Int8TensorwiseOps.lora_uses_rotated_input,
-                                                           nat.EPI_PYTORCH)
-                    elif rows > SMALL_BATCH_ROWS:
-                        y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
-                                                      nat.EPI_PYTORCH)
-                    else:
-                        if self._use_quarot:
-                            lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)
-                        w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
-                        y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
-                        if has_lora:
-                            lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
-                            F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)
+                if rows > SMALL_BATCH_ROWS and has_lora:
+                    # t = x @ A^T first; t @ B^T is accumulated inside the int8 GEMM kernel and added in its
+                    # epilogue with the reference's roundings: y = round(round(dequant + bias) + round(lora_y))
+                    lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype)
+                    y = custom_ops.linear_lora_forward(x2, weight, w_scale, bias, lora_a, lora_b, compute_dtype,
+                                                       self._use_quarot, Int8TensorwiseOps.lora_uses_rotated_input,
+                                                       nat.EPI_PYTORCH)
+                elif rows > SMALL_BATCH_ROWS:
+                    y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
+                                                  nat.EPI_PYTORCH)
+                else:
+                    y = self._small_batch_forward(x2, weight, w_scale, bias, lora_in, has_lora, compute_dtype)
 
                 if need_cast:
                     uncast_bias_weight(self, weight, bias, stream)
