@@ -246,12 +246,12 @@ def test_linear_traces_under_torch_compile(cuda_pkg, ops):
                             "bias": wl.bias_fp32(N, seed=21).bfloat16()}, K, N)
     x = wl.activation(48, K, seed=21).to(DEV)
     want = lin(x)
-    import torch._dynamo
-    torch._dynamo.reset()
+    from torch import _dynamo as dynamo
+    dynamo.reset()
     compiled = torch.compile(lin, backend="eager")
     assert torch.equal(compiled(x), want)
     a, b = wl.lora_factors(N, K, 8, seed=21)
     lin.lora_A, lin.lora_B = a.to(DEV), b.to(DEV)
     want = lin(x)
-    torch._dynamo.reset()
+    dynamo.reset()
     assert torch.equal(torch.compile(lin, backend="eager")(x), want)
