@@ -761,12 +761,143 @@ def run_merge(args):
                       "gpu_launches": args.steps * world, "clocks": clocks, "device_status": pkg._native.device_status()}))
 
 
+def run_small_batch(args):
+    """One step = one Linear call with M tokens <= 16 (a modulation-sized call: M=1, K=4096, N=24576) through the
+    tiny-batch branch: unquantised activations against int8 weights dequantised inside the kernel.  HBM-bound: the
+    algorithmic traffic is the int8 weights once, plus activations, bias and output."""
+    import torch
+    import __graft_entry__ as g
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    M, K, N = 1, 4096, 24576
+    bytes_step = float(N * K + 2 * M * K + 2 * N + 2 * M * N + 4)
+    pkg = g.load_package()
+    wl = pkg.workloads
+    n_sets = 8
+    cfg = {"workload": "small_batch_modulation_linear", "M_per_gpu": M, "K": K, "N": N, "weight_scale": "tensorwise",
+           "bias": True, "out_dtype": "bf16", "parallelism": f"independent calls x{world}",
+           "l2": f"weights rotate over {n_sets} buffers ({n_sets * N * K / 1e6:.0f} MB > 126 MB L2)"}
+    metric = "small_batch_linear_weight_bandwidth"
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import torch_path as tp
+        torch.set_num_threads(os.cpu_count() or 1)
+        x = wl.activation(M, K, seed=0)
+        wq, ws = tp.quantize_tensorwise(wl.weight_fp32(N, K, seed=0))
+        b = wl.bias_fp32(N, seed=0).bfloat16()
+        tp.linear_small_batch(x, wq, ws, b)
+        n = max(1, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            tp.linear_small_batch(x, wq, ws, b)
+        dt = (time.perf_counter() - t0) / n
+        base = {"value": bytes_step / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+                "sample": f"the full call, {n} passes of {dt * 1e3:.1f} ms"}
+        print(json.dumps({"impl": "reference", "metric": metric, "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
+                          "steps": n, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "cpu_baseline": base,
+                          "gpu_launches": 0,
+                          "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    F = pkg.functional
+    wq0, ws = F.quantize_tensorwise(wl.weight_fp32(N, K, seed=rank).to(dev))
+    ws = ws.reshape(1)
+    weights = [wq0.clone() for _ in range(n_sets)]
+    bias = wl.bias_fp32(N, seed=rank).bfloat16().to(dev)
+    x = wl.activation(M, K, seed=rank).to(dev)
+    steps = max(n_sets, (args.steps // n_sets) * n_sets)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(max(3, args.warmup)):
+            y = F.linear_small_batch(x, weights[i % n_sets], ws, bias)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(n_sets):
+                y = F.linear_small_batch(x, weights[i], ws, bias)
+    graph.replay()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0 = time.perf_counter()
+    a.record()
+    for _ in range(steps // n_sets):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    h1 = time.perf_counter()
+    ms = a.elapsed_time(b) / steps
+    clocks = sampler.stop(h0, h1) if sampler else None
+
+    # comparator (not the product path): the reference's expression with library kernels on this GPU
+    def torch_expression(w):
+        return torch.nn.functional.linear(x, (w.float() * ws).to(x.dtype), bias)
+    for i in range(3):
+        torch_expression(weights[i])
+    a.record()
+    for i in range(n_sets):
+        torch_expression(weights[i])
+    b.record()
+    torch.cuda.synchronize()
+    lib_ms = a.elapsed_time(b) / n_sets
+
+    # end to end: activations from pinned host memory, output back to the host, every step
+    x_host, y_host = x.cpu().pin_memory(), torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    e_steps = max(3, min(args.steps, 50))
+
+    def e2e_step(i):
+        y_host.copy_(F.linear_small_batch(x_host.to(dev, non_blocking=True), weights[i % n_sets], ws, bias), non_blocking=True)
+
+    e2e_step(0)
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(e_steps):
+        e2e_step(i)
+    b.record()
+    torch.cuda.synchronize()
+    e2e_ms = a.elapsed_time(b) / e_steps
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in t.tolist())
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    peaks, kind = measured_peaks()
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": metric, "value": world * achieved, "unit": "GB/s", "n_gpus": world, "steps": steps,
+                      "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+                      "roofline": {"bound": "hbm", "kernel": "small_m_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                                   "peak_source": f"hbm_gbs of {kind} MEASURED_PEAKS.json; launches replayed from a CUDA "
+                                                  f"graph of {n_sets}"},
+                      "library_expression_ms": lib_ms,
+                      "e2e": {"value": world * bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                              "h2d_bytes_per_step": 2 * M * K, "d2h_bytes_per_step": 2 * M * N, "steps": e_steps},
+                      "gpu_launches": steps * world, "clocks": clocks, "device_status": pkg._native.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     args = ap.parse_args()
@@ -778,6 +909,8 @@ def main():
         run_column_parallel(args)
     elif args.workload == "c2merge":
         run_merge(args)
+    elif args.workload == "smallm":
+        run_small_batch(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -57,6 +57,8 @@ _PROTOTYPES = {
                                    c_size_t, c_void_p]),
     "i8f_linear_forward_static": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                           c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "i8f_linear_w8a16_small": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                       c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "i8f_lora_down": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                               c_int64, c_void_p]),
     "i8f_lora_up": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,

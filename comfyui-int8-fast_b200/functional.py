@@ -204,6 +204,26 @@ def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype
     return out
 
 
+def linear_small_batch(x: Tensor, w: Tensor, w_scale, bias: Tensor | None) -> Tensor:
+    """M <= 16 rows: y = x @ dt(w.float() * w_scale)^T + dt(bias) in x's dtype (bf16 or fp16), activations not
+    quantised; one pass over the int8 weights instead of a dequantised copy of them."""
+    nat.require_device(x.device)
+    x, w = _rows(x), _rows(w)
+    M, K = x.shape
+    N = w.shape[0]
+    ws, mode = _wscale_arg(w_scale, x.device)
+    if bias is not None:
+        bias = bias.to(x.device).contiguous()
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if M == 0 or N == 0:
+        return out
+    nat.check(nat.load().i8f_linear_w8a16_small(nat.ptr(x), _code(x.dtype), _ld(x), nat.ptr(w), _ld(w), nat.ptr(ws), mode,
+                                                nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                                nat.ptr(out), N, M, N, K, nat.current_stream(x.device)),
+              "i8f_linear_w8a16_small")
+    return out
+
+
 def linear_forward_static(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out: Tensor, hadamard: bool = False,
                           order: int = nat.EPI_PYTORCH) -> Tensor:
     """linear_forward into a caller-supplied `out`, using the workspace built into the library.

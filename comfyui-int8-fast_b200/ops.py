@@ -509,12 +509,16 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
 
             @torch.compiler.disable
             def _small_batch_forward(self, x2, weight, w_scale, bias, lora_in, has_lora, compute_dtype):
-                """M <= 16 tokens: dequantised weights and a plain matmul, as the reference does (int8_quant.py:756-760)."""
+                """M <= 16 tokens: activations stay unquantised and meet the dequantised weights (int8_quant.py:756-760);
+                the weights are dequantised inside the kernel, never materialised."""
                 with torch.cuda.device(x2.device):
                     if self._use_quarot:
                         lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)
-                    w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
-                    y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
+                    if x2.dtype in (torch.bfloat16, torch.float16) and x2.shape[1] % 16 == 0:
+                        y = F.linear_small_batch(x2, weight, w_scale, bias)
+                    else:   # fp32 activations or an odd K: the reference's expression as it stands
+                        w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
+                        y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
                     if has_lora:
                         lora_a, lora_b = _prepare_lora(self, x2.device, compute_dtype)
                         F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)

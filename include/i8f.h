@@ -200,6 +200,18 @@ int i8f_linear_forward_static(const void* x, int x_dtype, int64_t ldx, int hadam
                               void* out, int out_dtype, int64_t ldo,
                               int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
+/* Linear for M <= 16 rows without activation quantisation (the tiny-batch branch of the Linear):
+ *   out [M,N] = round(x [M,K] @ dt(fp32(w) * w_scale)^T + dt(bias)),  dt = x_dtype (I8F_BF16 or I8F_F16),
+ * one pass over the int8 weights (HBM-bound on N*K bytes), fp32 accumulation, out in x_dtype.
+ * K and ldw multiples of 16, ldx a multiple of 8 elements, x and w 16-byte aligned; M > 16 returns
+ * I8F_ERR_UNSUPPORTED.  Replaces dequantize(weight, w_scale).to(x.dtype) + F.linear at int8_quant.py:756-760
+ * (which materialises the 16-bit weight matrix on every call). */
+int i8f_linear_w8a16_small(const void* x, int x_dtype, int64_t ldx,
+                           const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                           const void* bias, int bias_dtype,
+                           void* out, int64_t ldo,
+                           int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Dynamic-LoRA down projection: t [M,r] = round(x [M,K] @ lora_a [r,K]^T) in
  * `dtype` (I8F_BF16 or I8F_F16; x, lora_a and t share it), fp32 accumulation.
  * Replaces F.linear(x_2d, lora_A) at int8_quant.py:768. */

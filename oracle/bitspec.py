@@ -212,6 +212,23 @@ def linear_w8a8(x: np.ndarray, w_q: np.ndarray, w_scale, bias=None, *, act_dtype
 
 
 # --------------------------------------------------------------------------
+# Tiny-batch branch (M <= 16)                       int8_quant.py:756-760
+# --------------------------------------------------------------------------
+def linear_small_batch(x: np.ndarray, w_q: np.ndarray, w_scale, bias=None, dtype: str = "bf16") -> np.ndarray:
+    """y = rnd(x @ rnd(w.float() * scale)^T + rnd(bias)): the weights are dequantised to the activation dtype
+    (`dequantize(weight, w_scale).to(x.dtype)`, :757), the activations are NOT quantised, the matmul accumulates
+    in wider precision and rounds once (F.linear, :760).  Accumulated here in float64."""
+    scale = np.asarray(w_scale, dtype=F32)
+    if scale.ndim == 1 and scale.size > 1:
+        scale = scale.reshape(-1, 1)
+    w_f = round_to(dequantize(w_q, scale), dtype)
+    acc = np.asarray(x, dtype=F32).astype(np.float64) @ w_f.astype(np.float64).T
+    if bias is not None:
+        acc = acc + round_to(np.asarray(bias, dtype=F32), dtype).astype(np.float64)
+    return round_to(acc.astype(F32), dtype)
+
+
+# --------------------------------------------------------------------------
 # Dynamic LoRA                                      int8_quant.py:763-774
 # --------------------------------------------------------------------------
 def lora_down(x: np.ndarray, lora_a: np.ndarray, dtype: str = "bf16") -> np.ndarray:

@@ -84,6 +84,14 @@ def linear_w8a8(x: torch.Tensor, w_q: torch.Tensor, w_scale, bias, out_dtype: to
 
 
 @torch.no_grad()
+def linear_small_batch(x: torch.Tensor, w_q: torch.Tensor, w_scale, bias):
+    """The M <= 16 branch: dequantised weights in the activation dtype, a float matmul.   int8_quant.py:756-760"""
+    scale = w_scale.reshape(-1, 1) if isinstance(w_scale, torch.Tensor) and w_scale.numel() > 1 else w_scale
+    w_float = (w_q.float() * scale).to(x.dtype)
+    return torch.nn.functional.linear(x, w_float, bias.to(x.dtype) if bias is not None else None)
+
+
+@torch.no_grad()
 def lora_dynamic_add(y: torch.Tensor, x2: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor):
     """y + ((x @ A^T) @ B^T) with the adapter-dtype roundings.   int8_quant.py:763-774"""
     t = torch.nn.functional.linear(x2.to(lora_a.dtype), lora_a)

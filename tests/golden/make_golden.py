@@ -124,13 +124,16 @@ def main() -> None:
     lin._load_from_state_dict(sd, "", {}, True, [], [], [])
     x3 = x.reshape(4, 12, K)
     y_mod = lin(x3)
+    y_small_plain = lin(x3[:1, :8])   # M <= 16 without a LoRA: x @ bf16(w.float() * scale)^T + bias
+    y_one = lin(x3[2:3, 5:6])         # a single token
     lin.lora_A, lin.lora_B = lora_a, lora_b
     y_mod_lora = lin(x3)
     y_small = lin(x3[:1, :8])     # M <= 16: dequantised-weight branch
     np.savez_compressed(HERE / "module_small.npz", x_bits=bits(x), wq=wq_c.numpy(), ws=ws_c.numpy(),
                         bias_bits=bits(b.bfloat16()), lora_a_bits=bits(lora_a), lora_b_bits=bits(lora_b),
                         y_bits=bits(y_mod.reshape(M, N)), y_lora_bits=bits(y_mod_lora.reshape(M, N)),
-                        y_small_bits=bits(y_small.reshape(8, N)))
+                        y_small_bits=bits(y_small.reshape(8, N)), y_small_plain_bits=bits(y_small_plain.reshape(8, N)),
+                        y_one_bits=bits(y_one.reshape(1, N)))
 
     # ---- full-size CPU configuration, digests only ---------------------------
     M, K, N = 256, 3072, 3072

@@ -425,3 +425,49 @@ def test_bounded_wait_times_out_and_reports(cuda_pkg):
     got = cuda_pkg.functional.gemm_i8_i32(torch.ones(32, 64, dtype=torch.int8, device=DEV),
                                           torch.ones(16, 64, dtype=torch.int8, device=DEV))
     assert bool((got == 64).all())
+
+
+# ------------------------------------------------------------------ tiny-batch branch (M <= 16)
+@pytest.mark.parametrize("M,K,N,per_channel,bias_dt,dt", [
+    (1, 4096, 4096, False, torch.bfloat16, torch.bfloat16),     # a modulation-sized call
+    (8, 384, 72, True, torch.bfloat16, torch.bfloat16),
+    (16, 1024, 1000, True, torch.float32, torch.bfloat16),      # N not a multiple of the feature block
+    (9, 208, 333, False, None, torch.bfloat16),                 # K a multiple of 16 but not of 64, odd N
+    (3, 3072, 9216, True, torch.float16, torch.float16),
+    (13, 16, 5, True, torch.float32, torch.float16),
+    (2, 12288, 24576, False, torch.bfloat16, torch.bfloat16),   # widest feature block, several waves
+])
+def test_small_batch_linear_matches_oracle(cuda_pkg, M, K, N, per_channel, bias_dt, dt):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=41, dtype=dt)
+    w = wl.weight_fp32(N, K, seed=41).numpy()
+    wq, ws = (bs.quantize_rowwise if per_channel else bs.quantize_tensorwise)(w)
+    b = wl.bias_fp32(N, seed=41).to(bias_dt) if bias_dt is not None else None
+    want = bs.linear_small_batch(to_np(x), wq, ws, to_np(b) if b is not None else None, NAME[dt])
+    y = F.linear_small_batch(x.to(DEV), torch.from_numpy(wq).to(DEV), dev_ws(ws), b.to(DEV) if b is not None else None)
+    assert y.dtype == dt and y.shape == (M, N)
+    got = to_np(y)
+    # fp32 accumulation in a fixed order against float64: the rounded outputs differ on a few values, by one step
+    # of the output type (which at four sigma is itself above 1e-2 of the RMS for bf16, so the bar is per value),
+    # plus the fp32 accumulation error where the sum cancels
+    assert np.mean(got != want) <= 2e-2
+    step = np.abs(want) * (2.0 ** -7 if dt == torch.bfloat16 else 2.0 ** -10) + 1e-4 * rms(want)
+    assert np.all(np.abs(got - want) <= step)
+    assert rms(got - want) <= 1e-3 * rms(want)
+
+
+def test_small_batch_linear_is_deterministic_and_checks_arguments(cuda_pkg):
+    F, wl, nat = cuda_pkg.functional, cuda_pkg.workloads, cuda_pkg._native
+    x = wl.activation(16, 512, seed=5).to(DEV)
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(260, 512, seed=5).numpy())
+    wq, ws = torch.from_numpy(wq).to(DEV), dev_ws(ws)
+    a, b = F.linear_small_batch(x, wq, ws, None), F.linear_small_batch(x, wq, ws, None)
+    assert torch.equal(a, b)
+    # every row of a batch equals the same row computed alone (rows do not interact)
+    for m in (0, 7, 8, 15):
+        assert torch.equal(F.linear_small_batch(x[m:m + 1], wq, ws, None), a[m:m + 1])
+    assert F.linear_small_batch(x[:0], wq, ws, None).shape == (0, 260)
+    with pytest.raises(nat.NativeLibraryError):
+        F.linear_small_batch(wl.activation(17, 512, seed=5).to(DEV), wq, ws, None)       # M > 16
+    with pytest.raises(nat.NativeLibraryError):
+        F.linear_small_batch(x[:, :40].contiguous(), wq[:, :40].contiguous(), ws, None)   # K % 16 != 0

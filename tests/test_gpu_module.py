@@ -68,6 +68,12 @@ def test_module_forward_matches_reference_fixture(cuda_pkg, ops, golden):
     assert np.max(np.abs(to_np(y_small.reshape(8, N)) - want)) <= TOL * rms(want)
     lin.lora_A = lin.lora_B = None
     assert torch.equal(lin(x3), y)
+    # the same branch without a LoRA, eight tokens and a single one, against what the reference returned
+    for xs, key in ((x3[:1, :8], "y_small_plain_bits"), (x3[2:3, 5:6], "y_one_bits")):
+        want = bs.bf16_bits_to_f32(g[key])
+        got = to_np(lin(xs).reshape(-1, N))
+        assert np.max(np.abs(got - want)) <= TOL * rms(want)
+        assert np.mean(got != want) <= 2e-2
 
 
 def test_module_cast_path_and_fp32_input(cuda_pkg, ops):

@@ -108,6 +108,25 @@ def test_module_forward_with_dynamic_lora_matches_reference(golden):
     assert (bs.f32_to_bf16_bits(y2) != g["y_lora_bits"]).mean() <= 1e-2   # fp32 accumulation order inside the two GEMMs
 
 
+def test_small_batch_branch_matches_reference(golden):
+    """M <= 16: unquantised activations against dequantised weights.  The reference's CPU matmul accumulates in
+    its own order, so the bar is the output tolerance, and in fact at most one bf16 step on a few values."""
+    g = golden("module_small.npz")
+    x = f32(g["x_bits"]).reshape(4, 12, -1)
+    bias = f32(g["bias_bits"])
+    for xs, key in ((x[0, :8], "y_small_plain_bits"), (x[2, 5:6], "y_one_bits")):
+        ref = f32(g[key])
+        y = bs.linear_small_batch(xs, g["wq"], g["ws"], bias)
+        rms = np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+        assert np.max(np.abs(y - ref)) <= 1e-2 * rms
+        assert (bs.f32_to_bf16_bits(y) != g[key]).mean() <= 2e-2
+    # with the dynamic LoRA on top (the LoRA sees the same unquantised activations)
+    a, b = f32(g["lora_a_bits"]), f32(g["lora_b_bits"])
+    y = bs.lora_up_add(bs.linear_small_batch(x[0, :8], g["wq"], g["ws"], bias), bs.lora_down(x[0, :8], a), b)
+    ref = f32(g["y_small_bits"])
+    assert np.max(np.abs(y - ref)) <= 1e-2 * np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+
+
 def test_torch_path_equals_bitspec(pkg):
     wl = pkg.workloads
     x = wl.activation(40, 384, seed=3)
