@@ -14,8 +14,6 @@
 // A lane loads 16 consecutive weights of one row with one 128-bit load; the k index inside the MMA is a
 // permutation of the real one (lane t of a quad supplies real k = 16 t + 4 j + {0,1,2,3} to MMA j), applied to
 // x and w alike, so the sum is unchanged.
-#include <cstdlib>
-
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -137,7 +135,7 @@ small_m_kernel(const void* __restrict__ x, int64_t ldx, const int8_t* __restrict
                const float* __restrict__ w_scale, int per_row, const void* __restrict__ bias, int bias_dt,
                void* __restrict__ out, int64_t ldo, int M, int64_t N, int64_t K) {
     constexpr int kHalves = HI_ROWS ? 2 : 1;
-    __shared__ float4 s_part[kWarps][kHalves][32];
+    __shared__ float4 s_part[2][kWarps][kHalves][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int64_t n_blocks = (N + 15) / 16;
@@ -149,30 +147,37 @@ small_m_kernel(const void* __restrict__ x, int64_t ldx, const int8_t* __restrict
     const uint16_t* xb0 = xp + static_cast<int64_t>(g + 8 < M ? g + 8 : 0) * ldx + t * 16;
     constexpr int kStride = kWarps * 64;   // bytes of weights (elements of x) between a warp's chunks
 
-    for (int64_t nb = blockIdx.x; nb < n_blocks; nb += gridDim.x) {
-        float acc[kHalves][4];
-#pragma unroll
-        for (int h = 0; h < kHalves; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.0f;
+    // Per-lane pointers of a feature block: features g and g+8, this lane's 16-byte column, this warp's first chunk.
+    const int8_t *row_lo, *row_hi;
+    float sc_lo, sc_hi;
+    uint4 ring_lo[kDepth], ring_hi[kDepth];
+    auto open_block = [&](int64_t nb, float& s_lo, float& s_hi) {
         int64_t n_lo = nb * 16 + g, n_hi = n_lo + 8;
         n_lo = n_lo < N ? n_lo : N - 1;
         n_hi = n_hi < N ? n_hi : N - 1;
-        const int8_t* row_lo = w + n_lo * ldw + t * 16;
-        const int8_t* row_hi = w + n_hi * ldw + t * 16;
+        row_lo = w + n_lo * ldw + t * 16;
+        row_hi = w + n_hi * ldw + t * 16;
+#pragma unroll
+        for (int s = 0; s < kDepth; ++s) {
+            if (s < my_chunks) {
+                ring_lo[s] = __ldg(reinterpret_cast<const uint4*>(row_lo + warp * 64 + s * kStride));
+                ring_hi[s] = __ldg(reinterpret_cast<const uint4*>(row_hi + warp * 64 + s * kStride));
+            }
+        }
+        s_lo = per_row ? __ldg(w_scale + n_lo) : __ldg(w_scale);
+        s_hi = per_row ? __ldg(w_scale + n_hi) : s_lo;
+    };
+
+    int64_t nb = blockIdx.x;          // the grid never exceeds the number of blocks
+    open_block(nb, sc_lo, sc_hi);
+    for (int iter = 0;; ++iter) {
+        float acc[kHalves][4];
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.0f;
         const int8_t* wlo = row_lo + warp * 64;
         const int8_t* whi = row_hi + warp * 64;
         const uint16_t* xap = xa0 + warp * 64;
         const uint16_t* xbp = xb0 + warp * 64;
-
-        uint4 ring_lo[kDepth], ring_hi[kDepth];
-#pragma unroll
-        for (int s = 0; s < kDepth; ++s) {
-            if (s < my_chunks) {
-                ring_lo[s] = __ldg(reinterpret_cast<const uint4*>(wlo + s * kStride));
-                ring_hi[s] = __ldg(reinterpret_cast<const uint4*>(whi + s * kStride));
-            }
-        }
-        const float sc_lo = per_row ? __ldg(w_scale + n_lo) : __ldg(w_scale);
-        const float sc_hi = per_row ? __ldg(w_scale + n_hi) : sc_lo;
 
         for (int base = 0; base < my_chunks; base += kDepth) {
 #pragma unroll
@@ -208,15 +213,25 @@ small_m_kernel(const void* __restrict__ x, int64_t ldx, const int8_t* __restrict
             consume_chunk<DT, HI_ROWS>(tlo, thi, xf, sc_lo, sc_hi, acc);
         }
 
+        // the next block's first weights are in flight while this block's partial sums meet
+        const int64_t nb_next = nb + gridDim.x;
+        float next_lo = 0.0f, next_hi = 0.0f;
+        if (nb_next < n_blocks) open_block(nb_next, next_lo, next_hi);
+
+        // s_part is double-buffered, so one barrier per block is enough: a buffer is rewritten two blocks later, and
+        // every warp has passed the barrier in between only after the reader of the older block was done with it
+        const int buf = iter & 1;
 #pragma unroll
-        for (int h = 0; h < kHalves; ++h) s_part[warp][h][lane] = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+        for (int h = 0; h < kHalves; ++h)
+            s_part[buf][warp][h][lane] = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
         __syncthreads();
-        if (warp < kHalves) {
-            const int h = warp;
-            float4 s = s_part[0][h][lane];
+        const int first = (iter * kHalves) % kWarps;     // the summing duty rotates over the warps
+        if (warp >= first && warp < first + kHalves) {
+            const int h = warp - first;
+            float4 s = s_part[buf][0][h][lane];
 #pragma unroll
             for (int r = 1; r < kWarps; ++r) {
-                const float4 p = s_part[r][h][lane];
+                const float4 p = s_part[buf][r][h][lane];
                 s.x = __fadd_rn(s.x, p.x); s.y = __fadd_rn(s.y, p.y); s.z = __fadd_rn(s.z, p.z); s.w = __fadd_rn(s.w, p.w);
             }
             // accumulator fragment: (feature g, tokens 2t, 2t+1) and (feature g+8, same tokens)
@@ -231,7 +246,10 @@ small_m_kernel(const void* __restrict__ x, int64_t ldx, const int8_t* __restrict
                 }
             }
         }
-        __syncthreads();
+        if (nb_next >= n_blocks) break;
+        nb = nb_next;
+        sc_lo = next_lo;
+        sc_hi = next_hi;
     }
 }
 
@@ -243,17 +261,20 @@ int dispatch_small(const void* x, int64_t ldx, const int8_t* w, int64_t ldw, con
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t blocks = (N + 15) / 16;
-    const int grid = static_cast<int>(blocks < 16LL * sms ? blocks : 16LL * sms);   // the grid-stride loop takes the rest
-    int depth = 2;
-    if (const char* e = getenv("I8F_SMALL_DEPTH")) depth = atoi(e);   // experiments
-#define I8F_LAUNCH_SMALL(HI, D) \
-    small_m_kernel<DT, HI, D><<<grid, kThreads, 0, stream>>>(x, ldx, w, ldw, w_scale, per_row, bias, bias_dt, out, ldo, M, N, K)
-    if (M > 8) {
-        if (depth == 2) I8F_LAUNCH_SMALL(true, 2); else if (depth == 3) I8F_LAUNCH_SMALL(true, 3); else I8F_LAUNCH_SMALL(true, 4);
-    } else {
-        if (depth == 2) I8F_LAUNCH_SMALL(false, 2); else if (depth == 3) I8F_LAUNCH_SMALL(false, 3); else I8F_LAUNCH_SMALL(false, 4);
+    const bool hi = M > 8;
+    auto kernel = hi ? small_m_kernel<DT, true, 2> : small_m_kernel<DT, false, 2>;
+    // persistent: as many CTAs as are resident at once, each walking feature blocks with a grid stride
+    static int s_resident[2][2] = {};
+    int& per_sm = s_resident[DT == I8F_BF16 ? 0 : 1][hi ? 1 : 0];
+    if (per_sm == 0) {
+        int occ = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kThreads, 0);
+        if (e != cudaSuccess || occ < 1) return fail(I8F_ERR_CUDA, "small_m_kernel does not fit an SM");
+        per_sm = occ;
     }
-#undef I8F_LAUNCH_SMALL
+    const int64_t resident = static_cast<int64_t>(per_sm) * sms;
+    const int grid = static_cast<int>(blocks < resident ? blocks : resident);
+    kernel<<<grid, kThreads, 0, stream>>>(x, ldx, w, ldw, w_scale, per_row, bias, bias_dt, out, ldo, M, N, K);
     return check_launch("small_m_kernel");
 }
 
