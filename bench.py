@@ -96,7 +96,13 @@ class ClockSampler:
             return out
         self.stop_flag = True
         self.thread.join(timeout=2)
-        self.samples = [s for s in self.samples if t_begin <= s[3] <= t_end]
+        inside = [s for s in self.samples if t_begin <= s[3] <= t_end]
+        if not inside and self.samples:   # a timed region shorter than the sampling period: take the nearest sample
+            near = min(self.samples, key=lambda s: min(abs(s[3] - t_begin), abs(s[3] - t_end)))
+            out["note"] = (f"timed region shorter than the sampling period; nearest sample, "
+                           f"{min(abs(near[3] - t_begin), abs(near[3] - t_end)) * 1e3:.1f} ms away")
+            inside = [near]
+        self.samples = inside
         try:
             out["sm_max_mhz"] = float(self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
         except Exception:  # noqa: BLE001
