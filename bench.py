@@ -239,8 +239,16 @@ def run_gpu_arm(args):
                      "y_host": torch.empty((M, N), dtype=out_dtype).pin_memory()})
     gemm_events = []
 
+    workspace = torch.empty((nat.load().i8f_linear_workspace_bytes(M, K),), dtype=torch.uint8, device=dev)
+    EVENT_EVERY = 8   # the GEMM launch is bracketed by CUDA events on every 8th step of the timed region
+
     def step(i: int, timed: bool):
         s = sets[i % N_BUFFER_SETS]
+        if s["lora"] is None and not (timed and i % EVENT_EVERY == 0):
+            # the public fused call: K1 and K2 back to back on the stream (programmatic dependent launch), no events
+            return F.linear_forward(s["x"], s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard,
+                                    workspace=workspace)
+        timed = timed and (s["lora"] is not None or i % EVENT_EVERY == 0)
         q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
         # dynamic LoRA: t = x @ A^T, then the int8 GEMM accumulates t @ B^T in a second tensor-memory accumulator
         lora_t = F.lora_down(s["x"], s["lora"][0]) if s["lora"] is not None else None
@@ -362,7 +370,7 @@ def run_gpu_arm(args):
                      "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": NCU_GEMM_TRAFFIC_BYTES.get(shape.name),
                      "peak_source": f"2 x bf16_tflops (burst) of {peak_kind} MEASURED_PEAKS.json; int8 ops counted as 2*M*N*K",
                      "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "kernel_ms_avg": gemm_avg_ms,
-                     "kernel_ms_best": gemm_ms[0]},
+                     "kernel_ms_best": gemm_ms[0], "kernel_launches_timed": len(gemm_ms)},
         "cpu_baseline": cpu_base,
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                 "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},

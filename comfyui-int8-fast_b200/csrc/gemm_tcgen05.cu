@@ -38,7 +38,6 @@ namespace {
 
 constexpr int kBM = 128;            // rows of A per CTA == TMEM lanes
 constexpr int kStageRowBytes = 128; // one 128-byte swizzle span of K per stage
-constexpr int kThreads = 192;
 
 enum Kind : int { kKindI8 = 0, kKindBF16 = 1, kKindF16 = 2 };
 enum EpiMode : int { kEpiI32 = 0, kEpiDequant = 1, kEpiCast = 2, kEpiAccum = 3 };
@@ -92,17 +91,25 @@ struct Cfg {
     static constexpr int kABytes = kBM * kStageRowBytes;
     static constexpr int kBBytes = kBRows * kStageRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
-    // TMEM: two int32/fp32 accumulator buffers at columns 0 and BN; with LORA one more fp32 accumulator at 2*BN.
-    // The LoRA accumulator needs no double buffering: it is written at the very end of a tile's MMA sequence, long
-    // after the epilogue of the previous tile (which overlaps this tile's int8 K loop) has drained it.
-    static constexpr int kLoraCol = 2 * BN;
-    static constexpr int kColsUsed = LORA ? 3 * BN : 2 * BN;
+    // Epilogue warps: four (one per 32-lane quarter of tensor memory) or, where the epilogue cannot hide under the
+    // next tile's MMAs (single accumulator buffer, below), eight: two per quarter, each taking half of the columns.
+    static constexpr int kEpiWarps = (LORA && 3 * BN > 512) ? 8 : 4;
+    static constexpr int kThreads = 64 + 32 * kEpiWarps;
+    static constexpr int kRingBudget = (kEpiWarps == 8 ? 160 : 192) * 1024;   // eight warps need more staging space
+    static constexpr int kStages = kRingBudget / kStageBytes > 8 ? 8 : kRingBudget / kStageBytes;
+    // TMEM: two int32/fp32 accumulator buffers at columns 0 and BN, so the epilogue of a tile overlaps the MMAs of the
+    // next; with LORA one more fp32 accumulator behind them.  The LoRA accumulator needs no double buffering: it is
+    // written at the very end of a tile's MMA sequence, long after the epilogue of the previous tile has drained it.
+    // Three buffers of 256 columns do not fit the 512 columns: that configuration keeps ONE int32 buffer (the
+    // epilogue then runs between two tiles' MMAs instead of under them) and the full-rate 256-wide tile.
+    static constexpr int kAccBufs = (LORA && 3 * BN > 512) ? 1 : 2;
+    static constexpr int kLoraCol = kAccBufs * BN;
+    static constexpr int kColsUsed = (kAccBufs + (LORA ? 1 : 0)) * BN;
     static constexpr int kTmemCols = kColsUsed <= 128 ? 128 : (kColsUsed <= 256 ? 256 : 512);   // power of two >= 32
     static_assert(kColsUsed <= 512, "tensor memory has 512 columns");
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kEpiBytes = 4 * 2 * BN * 4;  // per epilogue warp: BN column scales + BN biases (fp32)
-    static constexpr int kOutStageBytes = 4 * 2 * 2048;  // per epilogue warp: two 32-row x 64-byte output chunks
+    static constexpr int kEpiBytes = kEpiWarps * 2 * BN * 4;  // per epilogue warp: BN column scales + BN biases (fp32)
+    static constexpr int kOutStageBytes = kEpiWarps * 2 * 2048;  // per epilogue warp: two 32-row x 64-byte output chunks
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + kEpiBytes + kOutStageBytes + 1024;  // + slack
     static constexpr int kTileM = PAIR ? 2 * kBM : kBM;
 };
@@ -150,31 +157,32 @@ __device__ __forceinline__ float load_as_f32(const void* p, int dt, long long i)
     return static_cast<const float*>(p)[i];
 }
 
-// Store 32 consecutive outputs of one row.  `y` already holds the values to
-// store (exactly representable in OUT when they were rounded by the caller).
-template <int OUT>
-__device__ __forceinline__ void store_row32(const GemmParams& p, long long row, int col, const float (&y)[32]) {
+// a + b on two packed 16-bit values, one rounding per lane.  Bit-identical to what the reference's tensor add does
+// (widen to fp32, add, round to the 16-bit type): the fp32 sum of two bf16 / fp16 values is either exact or so
+// lopsided that neither rounding can land on a tie.
+template <int DT>
+__device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    if constexpr (DT == I8F_BF16) {
+        const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    } else {
+        const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+}
+
+// Store 32 consecutive 16-bit outputs of one row, given as 16 packed pairs.
+__device__ __forceinline__ void store_row32(const GemmParams& p, long long row, int col, const uint32_t (&yp)[16]) {
     using T16 = unsigned short;
     T16* dst = static_cast<T16*>(p.out) + row * p.ldo + col;
     if (p.vec_ok && col + 32 <= p.N) {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack2<OUT>(y[8 * g + 0], y[8 * g + 1]);
-            o.y = pack2<OUT>(y[8 * g + 2], y[8 * g + 3]);
-            o.z = pack2<OUT>(y[8 * g + 4], y[8 * g + 5]);
-            o.w = pack2<OUT>(y[8 * g + 6], y[8 * g + 7]);
-            d4[g] = o;
-        }
+        for (int g = 0; g < 4; ++g) d4[g] = make_uint4(yp[4 * g], yp[4 * g + 1], yp[4 * g + 2], yp[4 * g + 3]);
     } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            if (col + j < p.N) {
-                const uint32_t w = pack2<OUT>(y[j], 0.f);
-                dst[j] = static_cast<T16>(w & 0xFFFFu);
-            }
-        }
+        for (int j = 0; j < 32; ++j)
+            if (col + j < p.N) dst[j] = static_cast<T16>((j & 1) ? (yp[j >> 1] >> 16) : (yp[j >> 1] & 0xFFFFu));
     }
 }
 
@@ -216,36 +224,40 @@ __device__ __forceinline__ void prefetch_old(const GemmParams& p, long long row,
 }
 
 template <int OUT>
-__device__ __forceinline__ void old_values(const GemmParams& p, long long row, int col, const OldChunk& o, float (&y)[32]) {
+__device__ __forceinline__ void old_values(const GemmParams& p, long long row, int col, const OldChunk& o, uint32_t (&yp)[16]) {
     if (o.valid) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const uint32_t w[4] = {o.raw[g].x, o.raw[g].y, o.raw[g].z, o.raw[g].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                y[8 * g + 2 * i] = unpack_lo<OUT>(w[i]);
-                y[8 * g + 2 * i + 1] = unpack_hi<OUT>(w[i]);
-            }
+            yp[4 * g] = o.raw[g].x;
+            yp[4 * g + 1] = o.raw[g].y;
+            yp[4 * g + 2] = o.raw[g].z;
+            yp[4 * g + 3] = o.raw[g].w;
         }
     } else {
+        float y[32];
         load_row32<OUT>(p, row, col, y);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) yp[i] = pack2<OUT>(y[2 * i], y[2 * i + 1]);   // exact: the values are 16-bit already
     }
 }
 
-// One 32-column chunk of one accumulator row.  `cs` / `cb` point at this chunk's 32 column scales and
-// biases in shared memory (the bias is already rounded to OUT when the reference order asks for it);
-// every lane reads the same address, a broadcast.  The result goes either straight to global memory or,
-// when `stage` is non-zero, into this warp's shared-memory staging chunk (row = lane, 64 bytes per row,
-// 16-byte pieces XOR-swizzled with (row >> 1) & 3 as the TMA 64-byte swizzle expects).
+// One 32-column chunk of one accumulator row.  `cs` points at this chunk's 32 column scales (fp32) in shared
+// memory; `cb` at its biases: 32 fp32 values for the single-rounding order, 16 packed pairs already rounded to
+// OUT for the reference order.  Every lane reads the same address, a broadcast.  In the reference order every
+// intermediate is a 16-bit tensor, so after the scaling the chunk lives as 16 packed pairs and each further
+// term (bias, LoRA, previous output) is one packed add per pair.  The result goes either straight to global
+// memory or, when `stage` is non-zero, into this warp's shared-memory staging chunk (row = lane, 64 bytes per
+// row, 16-byte pieces XOR-swizzled with (row >> 1) & 3 as the TMA 64-byte swizzle expects).
 template <int OUT, bool LORA>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, bool row_ok, int col,
                                                const uint32_t (&v)[32], const uint32_t (&lv)[LORA ? 32 : 1], float row_scale,
                                                float ws_scalar, const float* cs, const float* cb, const OldChunk& old,
                                                uint32_t stage, int lane, int wide_half = -1) {
-    float y[32];
+    uint32_t yp[16];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
         const bool single = p.epi_order == I8F_EPI_SINGLE;
+        float y[32];
         if (!per_ch) {
             // reference order: (ws * xs) first, then times the accumulator
             const float total = __fmul_rn(ws_scalar, row_scale);
@@ -260,37 +272,41 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
             for (int j = 0; j < 32; ++j)
                 y[j] = __fmul_rn(__int2float_rn(static_cast<int>(v[j])), __fmul_rn(row_scale, cs[j]));
         }
-        if (p.bias != nullptr) {
-            if (!single) {
+        if (single && p.bias != nullptr) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), cb[j]);
-            } else {
+            for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], cb[j]);
+        }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], cb[j]);
-            }
+        for (int i = 0; i < 16; ++i) yp[i] = pack2<OUT>(y[2 * i], y[2 * i + 1]);
+        if (!single && p.bias != nullptr) {
+            const uint32_t* cbp = reinterpret_cast<const uint32_t*>(cb);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) yp[i] = add2<OUT>(yp[i], cbp[i]);
         }
         if constexpr (LORA) {
-            // y + lora_y.to(y.dtype): both terms rounded to the output type first, as the reference does
+            // y + lora_y.to(y.dtype): both terms are in the output type, as in the reference
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), round_out<OUT>(__uint_as_float(lv[j])));
+            for (int i = 0; i < 16; ++i)
+                yp[i] = add2<OUT>(yp[i], pack2<OUT>(__uint_as_float(lv[2 * i]), __uint_as_float(lv[2 * i + 1])));
         }
         if (p.add_existing && row_ok) {
-            float prev[32];
+            uint32_t prev[16];
             old_values<OUT>(p, row, col, old, prev);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(round_out<OUT>(y[j]), prev[j]);
+            for (int i = 0; i < 16; ++i) yp[i] = add2<OUT>(yp[i], prev[i]);
         }
     } else if (p.epi_mode == kEpiCast) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+        for (int i = 0; i < 16; ++i) yp[i] = pack2<OUT>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
     } else {  // kEpiAccum: out = round(out + round(acc))
-        if (row_ok) old_values<OUT>(p, row, col, old, y);
+        if (row_ok) old_values<OUT>(p, row, col, old, yp);
         else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = 0.f;
+            for (int i = 0; i < 16; ++i) yp[i] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], round_out<OUT>(__uint_as_float(v[j])));
+        for (int i = 0; i < 16; ++i)
+            yp[i] = add2<OUT>(yp[i], pack2<OUT>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
     }
     if (stage != 0) {
         // narrow: 64-byte rows, 64-byte swizzle; wide (wide_half 0/1): this chunk is one half of a 128-byte row,
@@ -302,13 +318,12 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             const uint32_t a = row_addr + (((g0 + static_cast<uint32_t>(g)) ^ x) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<OUT>(y[8 * g + 0], y[8 * g + 1])),
-                         "r"(pack2<OUT>(y[8 * g + 2], y[8 * g + 3])), "r"(pack2<OUT>(y[8 * g + 4], y[8 * g + 5])),
-                         "r"(pack2<OUT>(y[8 * g + 6], y[8 * g + 7]))
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(yp[4 * g]), "r"(yp[4 * g + 1]),
+                         "r"(yp[4 * g + 2]), "r"(yp[4 * g + 3])
                          : "memory");
         }
     } else if (row_ok) {
-        store_row32<OUT>(p, row, col, y);
+        store_row32(p, row, col, yp);
     }
 }
 
@@ -326,7 +341,7 @@ __device__ __forceinline__ void store_i32_row32(const GemmParams& p, long long r
 }
 
 template <int KIND, int BN, bool PAIR, bool LORA>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Cfg<BN, PAIR, LORA>::kThreads), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ OutMaps outs, const __grid_constant__ LoraMaps lora, const GemmParams p) {
     using C = Cfg<BN, PAIR, LORA>;
@@ -363,7 +378,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(accfull0 + 8 * b, 1);
-            mbar_init(accempty0 + 8 * b, PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
+            mbar_init(accempty0 + 8 * b, (PAIR ? 2 : 1) * C::kEpiWarps);  // one arrival per epilogue warp (of both CTAs)
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -492,7 +507,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                                             : make_idesc(kDFmtF32, kFmtF16, C::kTileM, BN);
                     // the (single) LoRA accumulator was last read by the epilogue of the previous tile, which owns the
                     // other int32 buffer: its hand-back covers both.  Re-waiting a completed phase returns at once.
-                    if (t != tile_first) {
+                    if (C::kAccBufs == 2 && t != tile_first) {
                         const uint32_t prev_phase = (buf == 1) ? acc_phase : (acc_phase ^ 1u);
                         if (!mbar_wait_bounded(accempty0 + 8 * (buf ^ 1), prev_phase, abort_flag, p.status, kStAccEmptyWait)) break;
                         tc_fence_after_sync();
@@ -519,7 +534,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 if constexpr (PAIR) mma_commit_pair(accfull0 + 8 * buf);  // accumulator complete
                 else mma_commit(accfull0 + 8 * buf);
-                buf ^= 1;
+                if constexpr (C::kAccBufs == 2) buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }
         }
@@ -532,6 +547,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool dequant = p.epi_mode == kEpiDequant;
         const bool per_ch = dequant && p.w_scale_mode == I8F_WSCALE_CHANNEL;
         const bool has_bias = dequant && p.bias != nullptr;
+        const int bias_step = p.epi_order == I8F_EPI_PYTORCH ? 16 : 32;   // packed pairs or fp32 per 32-column chunk
         const float ws_scalar = (dequant && !per_ch) ? __ldg(p.w_scale) : 0.f;
         const uint32_t accempty_leader = PAIR ? mapa_cluster(accempty0, 0) : accempty0;
         const bool need_old = (dequant && p.add_existing) || p.epi_mode == kEpiAccum;
@@ -549,11 +565,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const int col = n_blk * BN + j;
                     const bool in = col < p.N;
                     if (per_ch) col_scale[j] = in ? __ldg(p.w_scale + col) : 0.f;
-                    if (has_bias) {
-                        float b = in ? load_as_f32(p.bias, p.bias_dtype, col) : 0.f;
-                        if (p.epi_order == I8F_EPI_PYTORCH)
-                            b = p.out_dtype == I8F_BF16 ? round_out<I8F_BF16>(b) : round_out<I8F_F16>(b);
-                        col_bias[j] = b;
+                    if (has_bias && p.epi_order != I8F_EPI_PYTORCH) col_bias[j] = in ? load_as_f32(p.bias, p.bias_dtype, col) : 0.f;
+                }
+                if (has_bias && p.epi_order == I8F_EPI_PYTORCH) {
+                    // the reference casts the bias to the output type and adds 16-bit tensors: keep it as packed pairs
+                    uint32_t* packed = reinterpret_cast<uint32_t*>(col_bias);
+                    for (int j = lane; j < BN / 2; j += 32) {
+                        const int col = n_blk * BN + 2 * j;
+                        const float b0 = col < p.N ? load_as_f32(p.bias, p.bias_dtype, col) : 0.f;
+                        const float b1 = col + 1 < p.N ? load_as_f32(p.bias, p.bias_dtype, col + 1) : 0.f;
+                        packed[j] = p.out_dtype == I8F_BF16 ? pack2<I8F_BF16>(b0, b1) : pack2<I8F_F16>(b0, b1);
                     }
                 }
                 __syncwarp();
@@ -562,23 +583,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const long long warp_row0 = row - lane;
             const bool row_ok = row < p.M;
             const float row_scale = (dequant && row_ok) ? __ldg(p.a_scale + row) : 0.f;
+            // this warp's share of the tile's 32-column chunks (all of them with four epilogue warps), cut at N
+            constexpr int kChunksPerWarp = (BN / 32) / (C::kEpiWarps / 4);
+            const int c_first = ((warp - 2) >> 2) * kChunksPerWarp;
+            const int chunks_in_n = static_cast<int>((p.N - static_cast<long long>(n_blk) * BN + 31) / 32);
+            const int c_end = min(c_first + kChunksPerWarp, chunks_in_n);
             OldChunk old_next;
             old_next.valid = false;
-            if (need_old) prefetch_old(p, row, row_ok, n_blk * BN, old_next);   // in flight while the MMAs finish
+            if (need_old && c_first < c_end)   // in flight while the MMAs finish
+                prefetch_old(p, row, row_ok, n_blk * BN + c_first * 32, old_next);
             if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
             tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
             const uint32_t t_lora = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(C::kLoraCol);
+            bool released = false;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = c_first; c < c_end; ++c) {
                 const int col = n_blk * BN + c * 32;
-                if (col >= p.N) break;                      // uniform over the CTA
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + c * 32, v);
                 uint32_t lv[LORA ? 32 : 1];
                 if constexpr (LORA) tmem_ld_32x32(t_lora + c * 32, lv);
                 const OldChunk old_cur = old_next;
-                if (need_old && c + 1 < BN / 32 && col + 32 < p.N) prefetch_old(p, row, row_ok, col + 32, old_next);
+                if (need_old && c + 1 < c_end) prefetch_old(p, row, row_ok, col + 32, old_next);
                 uint32_t stage = 0;
                 const int wide_half = wide_out ? (c & 1) : -1;
                 if (wide_out) {
@@ -596,14 +623,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     __syncwarp();
                 }
                 tmem_ld_wait();
+                if (c == c_end - 1) {
+                    // the last values of this warp's share are in registers: hand the accumulator back before the
+                    // arithmetic and the store of this chunk
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (PAIR) mbar_arrive_cluster(accempty_leader + 8 * buf);
+                        else mbar_arrive(accempty0 + 8 * buf);
+                    }
+                    released = true;
+                }
                 if (p.epi_mode == kEpiI32) {
                     if (row_ok) store_i32_row32(p, row, col, v);
                 } else if (p.out_dtype == I8F_BF16) {
                     epilogue_chunk<I8F_BF16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                   col_bias + c * 32, old_cur, stage, lane, wide_half);
+                                                   col_bias + c * bias_step, old_cur, stage, lane, wide_half);
                 } else {
                     epilogue_chunk<I8F_F16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                  col_bias + c * 32, old_cur, stage, lane, wide_half);
+                                                  col_bias + c * bias_step, old_cur, stage, lane, wide_half);
                 }
                 if (wide_out) {
                     if (wide_half == 1) {
@@ -627,13 +665,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     ++out_chunk;
                 }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(accempty_leader + 8 * buf);
-                else mbar_arrive(accempty0 + 8 * buf);
+            if (!released) {   // a warp whose share lies past N read nothing
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(accempty_leader + 8 * buf);
+                    else mbar_arrive(accempty0 + 8 * buf);
+                }
             }
-            buf ^= 1;
+            if constexpr (C::kAccBufs == 2) buf ^= 1;
             if (buf == 0) acc_phase ^= 1u;
         }
         if (tma_out && lane == 0) tma_store_wait_all<0>();   // shared memory must outlive the last store's reads
@@ -819,7 +859,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
         if (PAIR) {
             cudaLaunchConfig_t probe{};
             probe.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
-            probe.blockDim = dim3(kThreads, 1, 1);
+            probe.blockDim = dim3(C::kThreads, 1, 1);
             probe.dynamicSmemBytes = C::kSmemBytes;
             cudaLaunchAttribute at{};
             at.id = cudaLaunchAttributeClusterDimension;
@@ -837,7 +877,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     }
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     cudaLaunchConfig_t cfg{};
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = st;
     static const int use_pdl = [] {
@@ -1020,12 +1060,17 @@ int i8f_linear_w8a8_lora(const int8_t* a, int64_t lda, const float* a_scale, con
     p.epi_order = epilogue_order;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
     const LoraOperands lo{t, ldt, lora_b, ldb, r, out_dtype == I8F_BF16 ? kKindBF16 : kKindF16};
-    static const int bn160 = [] {
+    // tile width of the fused kernel: 256 (one int32 accumulator buffer, full-rate tile; default), 160 (double-buffered
+    // accumulators, narrower tile) or 128; I8F_LORA_BN selects the others for comparison
+    static const int bn = [] {
         const char* e = getenv("I8F_LORA_BN");
-        return (e != nullptr && e[0] == '1' && e[1] == '2') ? 0 : 1;   // I8F_LORA_BN=128 selects the narrower tile
+        const int v = e != nullptr ? atoi(e) : 256;
+        return (v == 128 || v == 160) ? v : 256;
     }();
-    if (bn160) return launch_gemm<kKindI8, 160, true, true>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), nullptr, &lo);
-    return launch_gemm<kKindI8, 128, true, true>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), nullptr, &lo);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (bn == 160) return launch_gemm<kKindI8, 160, true, true>(a, lda, w, ldw, M, N, K, p, st, nullptr, &lo);
+    if (bn == 128) return launch_gemm<kKindI8, 128, true, true>(a, lda, w, ldw, M, N, K, p, st, nullptr, &lo);
+    return launch_gemm<kKindI8, 256, true, true>(a, lda, w, ldw, M, N, K, p, st, nullptr, &lo);
 }
 
 int i8f_linear_w8a8_scatter(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
