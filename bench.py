@@ -29,7 +29,8 @@ sys.path.insert(0, str(ROOT))
 
 NOMINAL_INT8_TOPS = 4500.0   # B200 dense INT8, data-sheet
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the ncu capture summarised under profiles/
-NCU_GEMM_TRAFFIC_BYTES = {"c1_quarot_mlp_up": 184.7e6}
+NCU_GEMM_TRAFFIC_BYTES = {"c1_quarot_mlp_up": 184.6e6, "c2_dynamic_lora": 87.0e6}
+NCU_SMALL_M_TRAFFIC_BYTES = 104.6e6   # small_m_kernel at M=1, K=4096, N=24576
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 N_BUFFER_SETS = 4
 
@@ -897,7 +898,7 @@ def run_small_batch(args):
                       "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
                       "roofline": {"bound": "hbm", "kernel": "small_m_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                                   "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                                   "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_SMALL_M_TRAFFIC_BYTES,
                                    "peak_source": f"hbm_gbs of {kind} MEASURED_PEAKS.json; launches replayed from a CUDA "
                                                   f"graph of {n_sets}"},
                       "library_expression_ms": lib_ms,

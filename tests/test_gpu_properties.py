@@ -57,6 +57,28 @@ def test_linear_any_shape(cuda_pkg, M, kb, N, per_ch, use_bias, order, seed):
     assert np.array_equal(to_np(y), want)
 
 
+@settings(**COMMON)
+@given(M=st.integers(1, 16), kb=st.integers(1, 70), N=st.integers(1, 300), per_ch=st.booleans(), use_bias=st.booleans(),
+       dt=st.sampled_from(["bf16", "f16"]), seed=st.integers(0, 2 ** 16))
+def test_small_batch_linear_any_shape(cuda_pkg, M, kb, N, per_ch, use_bias, dt, seed):
+    """The tiny-batch branch over ragged K (any multiple of 16: full chunks, partial chunks, fewer chunks than warps),
+    any N (partial feature blocks) and every token count up to 16."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    K = 16 * kb
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    x = wl.activation(M, K, seed=seed, dtype=tdt)
+    w = wl.weight_fp32(N, K, seed=seed).numpy()
+    wq, ws = bs.quantize_rowwise(w) if per_ch else bs.quantize_tensorwise(w)
+    b = wl.bias_fp32(N, seed=seed) if use_bias else None
+    want = bs.linear_small_batch(to_np(x), wq, ws, None if b is None else b.numpy(), dt)
+    y = F.linear_small_batch(x.to(DEV), torch.from_numpy(wq).to(DEV), torch.from_numpy(np.asarray(ws, dtype=np.float32)).to(DEV),
+                             None if b is None else b.to(DEV))
+    got = to_np(y)
+    scale = float(np.sqrt(np.mean(want.astype(np.float64) ** 2))) + 1e-30
+    step = np.abs(want) * (2.0 ** -7 if dt == "bf16" else 2.0 ** -10) + 1e-4 * scale
+    assert np.all(np.abs(got - want) <= step)
+
+
 def test_status_word_is_clean_after_the_property_runs(cuda_pkg):
     torch.cuda.synchronize()
     assert cuda_pkg._native.device_status() == 0
