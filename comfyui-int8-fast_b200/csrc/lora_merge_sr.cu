@@ -27,23 +27,41 @@ __device__ __forceinline__ float load_f(const void* p, int dt, long long i) {
     return static_cast<const float*>(p)[i];
 }
 
-// Philox4x32-10, counter (c0, c1, 0, 0), key (k0, k1).
-__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
+// Philox4x32-10, counter (c0, c1, 0, 0).  The ten round keys (key + i * Weyl constants) depend on the seed only;
+// the host computes them once and they reach the kernel as launch parameters (constant bank operands).
+struct PhiloxKeys {
+    uint32_t k0[10], k1[10];
+};
+
+inline PhiloxKeys make_philox_keys(unsigned long long seed) {
+    PhiloxKeys k;
+    uint32_t a = static_cast<uint32_t>(seed), b = static_cast<uint32_t>(seed >> 32);
+    for (int i = 0; i < 10; ++i) {
+        k.k0[i] = a;
+        k.k1[i] = b;
+        a += 0x9E3779B9u;
+        b += 0xBB67AE85u;
+    }
+    return k;
+}
+
+__device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, const PhiloxKeys& key) {
     uint32_t x0 = c0, x1 = c1, x2 = 0u, x3 = 0u;
 #pragma unroll
     for (int i = 0; i < 10; ++i) {
-        const uint32_t hi0 = __umulhi(0xD2511F53u, x0), lo0 = 0xD2511F53u * x0;
-        const uint32_t hi1 = __umulhi(0xCD9E8D57u, x2), lo1 = 0xCD9E8D57u * x2;
-        const uint32_t n0 = hi1 ^ x1 ^ k0, n2 = hi0 ^ x3 ^ k1;
-        x0 = n0; x1 = lo1; x2 = n2; x3 = lo0;
-        k0 += 0x9E3779B9u;
-        k1 += 0xBB67AE85u;
+        const unsigned long long p0 = static_cast<unsigned long long>(0xD2511F53u) * x0;   // one wide multiply each
+        const unsigned long long p1 = static_cast<unsigned long long>(0xCD9E8D57u) * x2;
+        const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ x1 ^ key.k0[i];
+        const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ x3 ^ key.k1[i];
+        x0 = n0; x1 = static_cast<uint32_t>(p1); x2 = n2; x3 = static_cast<uint32_t>(p0);
     }
     return make_uint4(x0, x1, x2, x3);
 }
 __device__ __forceinline__ float u01(uint32_t w) { return static_cast<float>(w >> 8) * 5.9604644775390625e-8f; }
 
-// floor(x/ws) + [u < frac], clamped to int8 range.
+// floor(x/ws) + [u < frac], clamped to int8 range.  The IEEE division, floorf and the float->int conversion are
+// kept on purpose: a reciprocal-and-correct division and a magic-number floor were measured 1 - 3 % SLOWER here,
+// because they move work from the conversion pipe onto the ALU/FMA pipes this kernel already saturates.
 __device__ __forceinline__ int sr_round(float delta, float ws, float u) {
     const float xs = __fdiv_rn(delta, ws);
     const float fl = floorf(xs);
@@ -80,13 +98,48 @@ __device__ __forceinline__ int swz(int col) {
     return ((chunk ^ ((chunk >> 3) & 1)) << 2) | (col & 3);
 }
 
+// Byte `i` of a word, sign-extended: one byte permute whose upper three selectors replicate the sign of the byte
+// (selector nibble 8 | i; the __byte_perm intrinsic keeps only three bits per selector, so the PTX form is used).
+__device__ __forceinline__ int sext_byte(uint32_t word, int i) {
+    int v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(word), "r"(0u), "r"(0x8880u + 0x1111u * static_cast<uint32_t>(i)));
+    return v;
+}
+
+// Four ints -> four int8 in a word (byte 0 = a), each saturated to [-128, 127].
+__device__ __forceinline__ uint32_t pack4_sat(int a, int b, int c, int d) {
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(b), "r"(a), "r"(hi));
+    return w;
+}
+
+// The two 8-byte weight words and the row scales a thread will need in the tail, fetched at the top of a tile so
+// that the HBM latency passes under the rank-r product.
+struct TilePrefetch {
+    uint2 old[2];
+    float ws[2];
+    bool vec[2];   // old[i] holds the eight weights (row in range, full 8-byte aligned octet)
+};
+__device__ __forceinline__ void prefetch_tile(TilePrefetch& pf, const int8_t* __restrict__ w, long long ldw,
+                                              const float* __restrict__ w_scale, int ws_mode, int n_first, int row_end, int kc,
+                                              int K, int w_vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int n = n_first + i;
+        const bool in = n < row_end && kc < K;
+        pf.vec[i] = in && w_vec_ok && kc + 8 <= K;
+        pf.old[i] = pf.vec[i] ? *reinterpret_cast<const uint2*>(w + static_cast<long long>(n) * ldw + kc) : make_uint2(0u, 0u);
+        pf.ws[i] = in ? (ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale)) : 1.f;
+    }
+}
+
 // Shared tail of both merge kernels.  acc[i][c] is the un-scaled delta of row n_first + i, columns
 // kc..kc+7 (the thread's 2 x 8 patch; 16 adjacent lanes hold one 128-column block of a row).
 template <bool HAD>
-__device__ __forceinline__ void merge_tail(float (&acc)[2][8], int8_t* __restrict__ w, long long ldw,
-                                           const float* __restrict__ w_scale, int ws_mode, int n_first, int row_end, int kc,
-                                           int K, int lane, float lora_scale, const float* __restrict__ uniforms,
-                                           uint32_t key0, uint32_t key1, int w_vec_ok) {
+__device__ __forceinline__ void merge_tail(float (&acc)[2][8], int8_t* __restrict__ w, long long ldw, const TilePrefetch& pf,
+                                           int n_first, int row_end, int kc, int K, int lane, float lora_scale,
+                                           const float* __restrict__ uniforms, const PhiloxKeys& keys) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
 #pragma unroll
@@ -98,27 +151,28 @@ __device__ __forceinline__ void merge_tail(float (&acc)[2][8], int8_t* __restric
         }
         const int n = n_first + i;
         if (n >= row_end || kc >= K) continue;
-        const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
+        const float ws = pf.ws[i];
         float u[8];
         if (uniforms != nullptr) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) u[c] = (kc + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + kc + c) : 1.f;
         } else {
-            const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), key0, key1);
-            const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, key0, key1);
+            const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), keys);
+            const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, keys);
             u[0] = u01(ra.x); u[1] = u01(ra.y); u[2] = u01(ra.z); u[3] = u01(ra.w);
             u[4] = u01(rb.x); u[5] = u01(rb.y); u[6] = u01(rb.z); u[7] = u01(rb.w);
         }
         int8_t* wp = w + static_cast<long long>(n) * ldw + kc;
-        if (w_vec_ok && kc + 8 <= K) {
-            uint2 old = *reinterpret_cast<const uint2*>(wp);
-            uint32_t ow[2] = {old.x, old.y};
-            uint32_t nw[2] = {0u, 0u};
+        if (pf.vec[i]) {
+            const uint32_t ow[2] = {pf.old[i].x, pf.old[i].y};
+            uint32_t nw[2];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int wo = static_cast<int>(static_cast<int8_t>((ow[c >> 2] >> (8 * (c & 3))) & 0xFFu));
-                const int s = max(-128, min(127, wo + sr_round(acc[i][c], ws, u[c])));
-                nw[c >> 2] |= (static_cast<uint32_t>(s) & 0xFFu) << (8 * (c & 3));
+            for (int h = 0; h < 2; ++h) {
+                int v[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b)   // sign-extended byte b of the old word + the rounded delta
+                    v[b] = sext_byte(ow[h], b) + sr_round(acc[i][4 * h + b], ws, u[4 * h + b]);
+                nw[h] = pack4_sat(v[0], v[1], v[2], v[3]);    // the second clamp of the reference, as a saturating pack
             }
             *reinterpret_cast<uint2*>(wp) = make_uint2(nw[0], nw[1]);
         } else {
@@ -137,8 +191,8 @@ template <bool HAD>
 __global__ void __launch_bounds__(kThreads)
 lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict__ w_scale, int ws_mode,
                   const void* __restrict__ up, long long ldup, const void* __restrict__ down, long long lddown, int fdt,
-                  int N, int K, int r, float lora_scale, const float* __restrict__ uniforms, unsigned long long seed,
-                  int rows_per_cta, int w_vec_ok) {
+                  int N, int K, int r, float lora_scale, const float* __restrict__ uniforms,
+                  const __grid_constant__ PhiloxKeys keys, int rows_per_cta, int w_vec_ok) {
     extern __shared__ float smem[];
     float* s_down = smem;            // [r][128] swizzled
     float* s_up = smem + r * 128;    // [32][r + 1] (padded: the two row pairs of a warp land in different banks)
@@ -154,14 +208,14 @@ lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict
     const int tc = threadIdx.x & 15;   // column octet
     const int lane = threadIdx.x & 31;
     const int kc = k0 + tc * 8;
-    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
 
     for (int n0 = row_begin; n0 < row_end; n0 += kRowsPerIter) {
+        TilePrefetch pf;
+        prefetch_tile(pf, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, w_vec_ok);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < kRowsPerIter * r; idx += kThreads) {
-            const int rr = idx / r, j = idx - rr * r;
-            s_up[rr * rs + j] = (n0 + rr < row_end) ? load_f(up, fdt, static_cast<long long>(n0 + rr) * ldup + j) : 0.f;
-        }
+        for (int rr = threadIdx.x >> 5; rr < kRowsPerIter; rr += kThreads / 32)   // a warp per row: no index division
+            for (int j = threadIdx.x & 31; j < r; j += 32)
+                s_up[rr * rs + j] = (n0 + rr < row_end) ? load_f(up, fdt, static_cast<long long>(n0 + rr) * ldup + j) : 0.f;
         __syncthreads();
         float acc[2][8];
 #pragma unroll
@@ -182,8 +236,7 @@ lora_merge_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict
                 acc[1][c] = __fadd_rn(acc[1][c], __fmul_rn(ub, d[c]));
             }
         }
-        merge_tail<HAD>(acc, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, key0, key1,
-                        w_vec_ok);
+        merge_tail<HAD>(acc, w, ldw, pf, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, keys);
     }
 }
 
@@ -207,6 +260,13 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
     }
 }
 
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
 constexpr int kAccStride = 132;  // floats per row of the accumulator tile in shared memory
 
 template <bool HAD>
@@ -214,7 +274,8 @@ __global__ void __launch_bounds__(kThreads)
 lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restrict__ w_scale, int ws_mode,
                      const unsigned short* __restrict__ up, long long ldup, const unsigned short* __restrict__ down,
                      long long lddown, int is_bf16, int N, int K, int r, int r16, float lora_scale,
-                     const float* __restrict__ uniforms, unsigned long long seed, int rows_per_cta, int w_vec_ok) {
+                     const float* __restrict__ uniforms, const __grid_constant__ PhiloxKeys keys, int rows_per_cta,
+                     int w_vec_ok, int up_vec_ok) {
     extern __shared__ float smem[];
     const int rp = r16 + 8;                                        // padded rank (16-bit elements per row)
     float* s_acc = smem;                                            // [32][kAccStride] fp32
@@ -233,13 +294,30 @@ lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restr
     const int wm = (warp & 1) * 16;                                 // this warp's 16 rows ...
     const int wn = (warp >> 1) * 32;                                // ... and 32 columns of the tile
     const int kc = k0 + tc * 8;
-    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
 
     for (int n0 = row_begin; n0 < row_end; n0 += kRowsPerIter) {
+        TilePrefetch pf;
+        prefetch_tile(pf, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, w_vec_ok);
         __syncthreads();                                            // previous tile fully consumed (s_up, s_acc)
-        for (int idx = threadIdx.x; idx < kRowsPerIter * r16; idx += kThreads) {
-            const int rr = idx / r16, j = idx - rr * r16;
-            s_up[rr * rp + j] = (j < r && n0 + rr < row_end) ? up[static_cast<long long>(n0 + rr) * ldup + j] : 0;
+        // rows of `up` into shared memory: a warp takes rows warp, warp + 8, ...; a lane one 8-element (16-byte) piece of
+        // a row, so there is no index division in the loop.  Pieces past the rank, rows past the band: zeros.
+        for (int rr = warp; rr < kRowsPerIter; rr += kThreads / 32) {
+            const bool row_in = n0 + rr < row_end;
+            const unsigned short* src = up + static_cast<long long>(n0 + rr) * ldup;
+            for (int j = lane * 8; j < r16; j += 256) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (row_in) {
+                    if (up_vec_ok && j + 8 <= r) {
+                        v = __ldg(reinterpret_cast<const uint4*>(src + j));
+                    } else {
+                        unsigned short e[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) e[q] = (j + q < r) ? src[j + q] : static_cast<unsigned short>(0);
+                        v = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+                    }
+                }
+                *reinterpret_cast<uint4*>(s_up + rr * rp + j) = v;   // rp is a multiple of 8: 16-byte aligned
+            }
         }
         __syncthreads();
         float d[4][4];
@@ -247,20 +325,20 @@ lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restr
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) d[nt][e] = 0.f;
+        // fragments by ldmatrix: one x4 for the 16 x 16 piece of `up`, one x4 per pair of 8-column groups of `down`
+        // (rows of both tiles are rp * 2 bytes apart, an odd multiple of 16 bytes: conflict free)
+        const uint32_t a_addr = smem_addr(s_up + (wm + (lane & 15)) * rp + ((lane >> 4) << 3));
+        const uint32_t b_addr = smem_addr(s_downT + (wn + (lane & 7) + ((lane >> 4) << 3)) * rp + (((lane >> 3) & 1) << 3));
         for (int kk = 0; kk < r16; kk += 16) {
             uint32_t a[4];
-            const unsigned short* ar = s_up + (wm + g) * rp + kk + 2 * t4;
-            a[0] = *reinterpret_cast<const uint32_t*>(ar);
-            a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * rp);
-            a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * rp + 8);
+            ldmatrix_x4(a, a_addr + kk * 2);
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                uint32_t b[2];
-                const unsigned short* br = s_downT + (wn + nt * 8 + g) * rp + kk + 2 * t4;
-                b[0] = *reinterpret_cast<const uint32_t*>(br);
-                b[1] = *reinterpret_cast<const uint32_t*>(br + 8);
-                mma_16816(d[nt], a, b, is_bf16 != 0);
+            for (int np = 0; np < 2; ++np) {
+                uint32_t b[4];   // {k 0-7, k 8-15} of columns 16 np .. 16 np + 7, then of 16 np + 8 .. 16 np + 15
+                ldmatrix_x4(b, b_addr + (np * 16 * rp + kk) * 2);
+                const uint32_t b_lo[2] = {b[0], b[1]}, b_hi[2] = {b[2], b[3]};
+                mma_16816(d[2 * np], a, b_lo, is_bf16 != 0);
+                mma_16816(d[2 * np + 1], a, b_hi, is_bf16 != 0);
             }
         }
 #pragma unroll
@@ -278,8 +356,7 @@ lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restr
             acc[i][0] = lo.x; acc[i][1] = lo.y; acc[i][2] = lo.z; acc[i][3] = lo.w;
             acc[i][4] = hi.x; acc[i][5] = hi.y; acc[i][6] = hi.z; acc[i][7] = hi.w;
         }
-        merge_tail<HAD>(acc, w, ldw, w_scale, ws_mode, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, key0, key1,
-                        w_vec_ok);
+        merge_tail<HAD>(acc, w, ldw, pf, n0 + 2 * tr, row_end, kc, K, lane, lora_scale, uniforms, keys);
     }
 }
 
@@ -288,10 +365,9 @@ lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restr
 __global__ void __launch_bounds__(kThreads)
 stochastic_round_kernel(const float* __restrict__ delta, long long ldd, const float* __restrict__ w_scale, int ws_mode,
                         int8_t* __restrict__ d8, long long ldq, int N, int K, const float* __restrict__ uniforms,
-                        unsigned long long seed) {
+                        const __grid_constant__ PhiloxKeys keys) {
     const int groups = (K + 3) >> 2;
     const long long total = static_cast<long long>(N) * groups;
-    const uint32_t key0 = static_cast<uint32_t>(seed), key1 = static_cast<uint32_t>(seed >> 32);
     for (long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; g < total;
          g += static_cast<long long>(gridDim.x) * kThreads) {
         const int n = static_cast<int>(g / groups);
@@ -302,7 +378,7 @@ stochastic_round_kernel(const float* __restrict__ delta, long long ldd, const fl
 #pragma unroll
             for (int c = 0; c < 4; ++c) u[c] = (4 * kg + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + 4 * kg + c) : 1.f;
         } else {
-            const uint4 rr = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kg), key0, key1);
+            const uint4 rr = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kg), keys);
             u[0] = u01(rr.x); u[1] = u01(rr.y); u[2] = u01(rr.z); u[3] = u01(rr.w);
         }
 #pragma unroll
@@ -363,7 +439,8 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
             kern<<<grid, kThreads, smem, st>>>(w, ldw, w_scale, w_scale_mode, static_cast<const unsigned short*>(up), ldup,
                                                static_cast<const unsigned short*>(down), lddown,
                                                factor_dtype == I8F_BF16 ? 1 : 0, static_cast<int>(N), static_cast<int>(K),
-                                               static_cast<int>(r), r16, lora_scale, uniforms, seed, rows_per_cta, w_vec_ok);
+                                               static_cast<int>(r), r16, lora_scale, uniforms, make_philox_keys(seed), rows_per_cta, w_vec_ok,
+                                               ((reinterpret_cast<uintptr_t>(up) & 15u) == 0 && ldup % 8 == 0) ? 1 : 0);
             return check_launch("lora_merge_tc_kernel");
         };
         return hadamard128 ? launch_tc(lora_merge_tc_kernel<true>) : launch_tc(lora_merge_tc_kernel<false>);
@@ -375,7 +452,7 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
         }
         kern<<<grid, kThreads, smem, st>>>(w, ldw, w_scale, w_scale_mode, up, ldup, down, lddown, factor_dtype,
                                            static_cast<int>(N), static_cast<int>(K), static_cast<int>(r), lora_scale,
-                                           uniforms, seed, rows_per_cta, w_vec_ok);
+                                           uniforms, make_philox_keys(seed), rows_per_cta, w_vec_ok);
         return check_launch("lora_merge_kernel");
     };
     return hadamard128 ? launch(lora_merge_kernel<true>) : launch(lora_merge_kernel<false>);
@@ -394,7 +471,7 @@ int i8f_stochastic_round(const float* delta, int64_t ldd, const float* w_scale, 
     long long blocks = (total + kThreads - 1) / kThreads;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
     stochastic_round_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        delta, ldd, w_scale, w_scale_mode, d8, ldq, static_cast<int>(N), static_cast<int>(K), uniforms, seed);
+        delta, ldd, w_scale, w_scale_mode, d8, ldq, static_cast<int>(N), static_cast<int>(K), uniforms, make_philox_keys(seed));
     return check_launch("stochastic_round_kernel");
 }
 
