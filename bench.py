@@ -249,7 +249,11 @@ def run_gpu_arm(args):
             # the public fused call: K1 and K2 back to back on the stream (programmatic dependent launch), no events
             return F.linear_forward(s["x"], s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard,
                                     workspace=workspace)
-        timed = timed and (s["lora"] is not None or i % EVENT_EVERY == 0)
+        if s["lora"] is not None and not (timed and i % EVENT_EVERY == 0):
+            # the public fused-LoRA op: K1 and the LoRA down projection overlap on two streams, then the fused GEMM
+            return pkg.custom_ops.linear_lora_forward(s["x"], s["wq"], s["ws"], s["bias"], s["lora"][0], s["lora"][1], out_dtype,
+                                                      shape.hadamard, False, nat.EPI_PYTORCH)
+        timed = timed and i % EVENT_EVERY == 0
         q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
         # dynamic LoRA: t = x @ A^T, then the int8 GEMM accumulates t @ B^T in a second tensor-memory accumulator
         lora_t = F.lora_down(s["x"], s["lora"][0]) if s["lora"] is not None else None
