@@ -112,6 +112,53 @@ __device__ __forceinline__ void wht128(float (&v)[8], int lane) {
     }
 }
 
+// The same 128-point butterfly for a block held by FOUR lanes x four vectors x 8 registers (element index =
+// ((c * 4 + l) * 8 + r) for vector c, lane l of the quad, register r): strides 1, 2, 4 inside a vector, strides 8, 16
+// across the quad (two shuffle stages instead of four), strides 32, 64 across the thread's vectors.  Same stage
+// order and the same a+b / a-b assignment as wht128, hence the same bits.
+__device__ __forceinline__ void wht128_quad(float (&v)[4][8], int lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if ((i & h) == 0) {
+                    const float a = v[c][i], b = v[c][i + h];
+                    v[c][i] = __fadd_rn(a, b);
+                    v[c][i + h] = __fsub_rn(a, b);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 1; d < 4; d <<= 1) {
+        const float s = (lane & d) != 0 ? -1.0f : 1.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float p = __shfl_xor_sync(0xFFFFFFFFu, v[c][i], d);
+                v[c][i] = __fmaf_rn(s, v[c][i], p);
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 1; h < 4; h <<= 1) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if ((c & h) == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float a = v[c][i], b = v[c + h][i];
+                    v[c][i] = __fadd_rn(a, b);
+                    v[c + h][i] = __fsub_rn(a, b);
+                }
+            }
+        }
+    }
+}
+
 // Four values -> four int8 packed in a word.  y = x*inv is rounded to the nearest-even integer by
 // adding 1.5*2^23 (the sum's low mantissa bits then hold the two's-complement integer), which is
 // rint(y) for |y| < 2^22; here |y| <= 127.00002 by construction of the scale, so no clamp is needed.
@@ -143,10 +190,19 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
     const bool row_ok = row < M;
     const int nvec = static_cast<int>(K >> 3);
 
+    // Which 8-element vector of the row sits in slot i of this thread.  Plain layout: vectors t, t + tpr, ... (a warp
+    // load covers 512 contiguous bytes).  With the rotation and at least four vectors per thread, a 128-element
+    // block belongs to a QUAD of lanes instead of sixteen: slot i = 4 s + c holds chunk 4 c + (t & 3) of block
+    // s * tpr / 4 + t / 4, so a warp load covers eight 64-byte pieces and the butterfly needs half the shuffles.
+    constexpr bool kQuad = HAD && (VPT % 4 == 0);
+    auto vec_of = [&](int i) -> int {
+        if constexpr (kQuad) return (((i >> 2) * (tpr >> 2) + (t >> 2)) << 4) + ((i & 3) << 2) + (t & 3);
+        else return i * tpr + t;
+    };
     float v[VPT][8];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int vec = i * tpr + t;
+        const int vec = vec_of(i);
         if (row_ok && vec < nvec) {
             load8<DT>(x, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
         } else {
@@ -157,16 +213,20 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
 
     if constexpr (HAD) {
         constexpr float norm = (ROT_F32 || DT == I8F_F32) ? kNormF32 : kNormHalf;
+        if constexpr (kQuad) {
+#pragma unroll
+            for (int sgrp = 0; sgrp < VPT / 4; ++sgrp) wht128_quad(*reinterpret_cast<float(*)[4][8]>(&v[4 * sgrp]), lane);
+        }
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            wht128(v[i], lane);
+            if constexpr (!kQuad) wht128(v[i], lane);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float r = __fmul_rn(v[i][j], norm);
                 v[i][j] = ROT_F32 ? r : round_to_dt<DT>(r);
             }
             if constexpr (MODE == kRowwise) {
-                const int vec = i * tpr + t;
+                const int vec = vec_of(i);
                 if (xrot != nullptr && row_ok && vec < nvec) store8<DT>(xrot, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
             }
         }
@@ -214,7 +274,7 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int vec = i * tpr + t;
+        const int vec = vec_of(i);
         if (row_ok && vec < nvec) {
             uint2 o;
             o.x = quant4(v[i][0], v[i][1], v[i][2], v[i][3], inv);
