@@ -79,17 +79,27 @@ def bf16_linear(in_f: int, out_f: int, gen: torch.Generator, device) -> nn.Linea
 
 
 def rms_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
-    return (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    return TF.rms_norm(x, x.shape[-1:], eps=eps)
 
 
 def modulate(x: Tensor, shift: Tensor, scale: Tensor) -> Tensor:
-    return TF.layer_norm(x, x.shape[-1:]) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+    """LayerNorm(x) * (1 + scale) + shift, the scale-and-shift as one pass over the normalised tensor."""
+    return torch.addcmul(shift.unsqueeze(1), TF.layer_norm(x, x.shape[-1:]), 1 + scale.unsqueeze(1))
 
 
-def attention(q: Tensor, k: Tensor, v: Tensor, heads: int) -> Tensor:
-    b, t, h = q.shape
-    q, k, v = (z.view(b, t, heads, h // heads).transpose(1, 2) for z in (q, k, v))
-    return TF.scaled_dot_product_attention(rms_norm(q), rms_norm(k), v).transpose(1, 2).reshape(b, t, h)
+def gated_residual(x: Tensor, gate: Tensor, y: Tensor) -> Tensor:
+    """x + gate * y in one pass."""
+    return torch.addcmul(x, gate.unsqueeze(1), y)
+
+
+def attention(qkv: Tensor, heads: int) -> Tensor:
+    """qkv [B, T, 3*h] (q | k | v along the last axis) -> [B, T, h].  q and k are RMS-normalised per head; all three
+    go to the attention kernel as [B, heads, T, d] views of the token-major buffers (no transposed copies)."""
+    b, t, h3 = qkv.shape
+    h = h3 // 3
+    q, k, v = qkv.view(b, t, 3, heads, h // heads).unbind(2)
+    out = TF.scaled_dot_product_attention(rms_norm(q).transpose(1, 2), rms_norm(k).transpose(1, 2), v.transpose(1, 2))
+    return out.transpose(1, 2).reshape(b, t, h)
 
 
 class StreamBlock(nn.Module):
@@ -118,14 +128,13 @@ class DoubleBlock(nn.Module):
         qkv = {}
         for name, x, blk in (("txt", txt, self.txt), ("img", img, self.img)):
             mods[name] = blk.mod(TF.silu(vec)).chunk(6, dim=-1)
-            qkv[name] = blk.qkv(modulate(x, mods[name][0], mods[name][1])).chunk(3, dim=-1)
-        q, k, v = (torch.cat([qkv["txt"][i], qkv["img"][i]], dim=1) for i in range(3))
-        attn = attention(q, k, v, cfg.heads)
+            qkv[name] = blk.qkv(modulate(x, mods[name][0], mods[name][1]))
+        attn = attention(torch.cat([qkv["txt"], qkv["img"]], dim=1), cfg.heads)   # joint attention over text + image
         outs = []
         for name, x, blk, a in (("txt", txt, self.txt, attn[:, : txt.shape[1]]), ("img", img, self.img, attn[:, txt.shape[1]:])):
             sh1, sc1, g1, sh2, sc2, g2 = mods[name]
-            x = x + g1.unsqueeze(1) * blk.proj(a)
-            x = x + g2.unsqueeze(1) * blk.mlp_down(TF.gelu(blk.mlp_up(modulate(x, sh2, sc2)), approximate="tanh"))
+            x = gated_residual(x, g1, blk.proj(a))
+            x = gated_residual(x, g2, blk.mlp_down(TF.gelu(blk.mlp_up(modulate(x, sh2, sc2)), approximate="tanh")))
             outs.append(x)
         return outs[1], outs[0]
 
@@ -143,9 +152,11 @@ class SingleBlock(nn.Module):
         h = self.cfg.hidden
         shift, scale, gate = self.mod(TF.silu(vec)).chunk(3, dim=-1)
         y = self.linear1(modulate(x, shift, scale))
-        q, k, v, mlp = y[..., :h], y[..., h:2 * h], y[..., 2 * h:3 * h], y[..., 3 * h:]
-        a = attention(q, k, v, self.cfg.heads)
-        return x + gate.unsqueeze(1) * self.linear2(torch.cat([a, TF.gelu(mlp, approximate="tanh")], dim=-1))
+        # attention output and the activated MLP half go side by side into one buffer (no concatenation pass)
+        z = torch.empty(y.shape[:-1] + (y.shape[-1] - 2 * h,), dtype=y.dtype, device=y.device)
+        z[..., :h] = attention(y[..., :3 * h], self.cfg.heads)
+        torch.ops.aten.gelu.out(y[..., 3 * h:], approximate="tanh", out=z[..., h:])
+        return gated_residual(x, gate, self.linear2(z))
 
 
 def timestep_embedding(t: Tensor, dim: int = 256) -> Tensor:
