@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory by EXECUTING THE REFERENCE.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
-The reference project (default /root/reference) is imported as a package with
+The reference project (a checkout of ComfyUI-INT8-Fast) is imported as a package with
 the test-only fake `comfy` on sys.path, and its own functions are run on CPU
 tensors built from the seeded recipes in the package's workloads module:
 
@@ -54,7 +54,9 @@ def sha(a: np.ndarray) -> str:
 
 
 def main() -> None:
-    ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/the/reference/checkout")
+    ref_path = sys.argv[1]
     rq, rr = load_reference(ref_path)
     import __graft_entry__ as g  # noqa: PLC0415
     wl = g.load_package().workloads
