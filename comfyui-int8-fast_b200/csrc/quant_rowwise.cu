@@ -53,6 +53,23 @@ __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float 
     }
 }
 
+// Eight 16-bit values held as loaded (four words) -> eight floats.
+template <int DT>
+__device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (DT == I8F_BF16) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+}
+
 // Round an fp32 value to the storage type and return it as fp32.
 template <int DT>
 __device__ __forceinline__ float round_to_dt(float x) {
@@ -199,15 +216,32 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
         if constexpr (kQuad) return (((i >> 2) * (tpr >> 2) + (t >> 2)) << 4) + ((i & 3) << 2) + (t & 3);
         else return i * tpr + t;
     };
-    float v[VPT][8];
+    // Without the rotation a 16-bit row stays in registers AS LOADED (four words per vector instead of eight floats)
+    // until it is quantised: half the registers, so long rows (8 or 16 vectors per thread) keep 4 / 2 CTAs per SM
+    // instead of 2 / 1.  The row maximum is taken on the packed values: non-negative bf16 / fp16 order like their
+    // bit patterns, so it is a 16-bit unsigned SIMD max after clearing the sign bits.
+    constexpr bool kPacked = !HAD && DT != I8F_F32;
+    float v[kPacked ? 1 : VPT][8];
+    uint4 raw[kPacked ? VPT : 1];
+    if constexpr (kPacked) {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int vec = vec_of(i);
-        if (row_ok && vec < nvec) {
-            load8<DT>(x, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
-        } else {
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = vec_of(i);
+            raw[i] = (row_ok && vec < nvec)
+                         ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx +
+                                                                static_cast<int64_t>(vec) * 8))
+                         : make_uint4(0u, 0u, 0u, 0u);
+        }
+    } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = vec_of(i);
+            if (row_ok && vec < nvec) {
+                load8<DT>(x, row * ldx + static_cast<int64_t>(vec) * 8, v[i]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+            }
         }
     }
 
@@ -234,10 +268,24 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
 
     float amax = 0.f;
     if constexpr (MODE != kGlobalScale) {
+        if constexpr (kPacked) {
+            uint32_t m2 = 0u;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i)
+            for (int i = 0; i < VPT; ++i) {
+                m2 = __vmaxu2(m2, raw[i].x & 0x7FFF7FFFu);
+                m2 = __vmaxu2(m2, raw[i].y & 0x7FFF7FFFu);
+                m2 = __vmaxu2(m2, raw[i].z & 0x7FFF7FFFu);
+                m2 = __vmaxu2(m2, raw[i].w & 0x7FFF7FFFu);
+            }
+            const uint32_t m16 = max(m2 & 0xFFFFu, m2 >> 16);
+            if constexpr (DT == I8F_BF16) amax = __uint_as_float(m16 << 16);
+            else amax = __half2float(__ushort_as_half(static_cast<unsigned short>(m16)));
+        } else {
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) amax = fmaxf(fmaxf(amax, fabsf(v[i][j])), fabsf(v[i][j + 1]));
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) amax = fmaxf(fmaxf(amax, fabsf(v[i][j])), fabsf(v[i][j + 1]));
+        }
         // reduce over the lanes of this row that share a warp
         // (the whole warp when only the tensor-wide maximum is wanted)
         const int span = (MODE == kAbsmaxOnly || tpr > 32) ? 32 : tpr;
@@ -276,9 +324,16 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
     for (int i = 0; i < VPT; ++i) {
         const int vec = vec_of(i);
         if (row_ok && vec < nvec) {
+            float f[8];
+            if constexpr (kPacked) {
+                unpack8<DT>(raw[i], f);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = v[i][j];
+            }
             uint2 o;
-            o.x = quant4(v[i][0], v[i][1], v[i][2], v[i][3], inv);
-            o.y = quant4(v[i][4], v[i][5], v[i][6], v[i][7], inv);
+            o.x = quant4(f[0], f[1], f[2], f[3], inv);
+            o.y = quant4(f[4], f[5], f[6], f[7], inv);
             *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = o;
         }
     }
