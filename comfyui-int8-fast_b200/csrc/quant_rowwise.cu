@@ -53,6 +53,18 @@ __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float 
     }
 }
 
+// Two floats rounded (nearest even) to the 16-bit type DT, packed in a word (a in the low half).
+template <int DT>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (DT == I8F_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
 // Eight 16-bit values held as loaded (four words) -> eight floats.
 template <int DT>
 __device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]) {
@@ -220,7 +232,9 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
     // until it is quantised: half the registers, so long rows (8 or 16 vectors per thread) keep 4 / 2 CTAs per SM
     // instead of 2 / 1.  The row maximum is taken on the packed values: non-negative bf16 / fp16 order like their
     // bit patterns, so it is a 16-bit unsigned SIMD max after clearing the sign bits.
-    constexpr bool kPacked = !HAD && DT != I8F_F32;
+    // The same holds with the activation rule of the rotation, whose result is rounded to the 16-bit type anyway:
+    // the row is loaded packed, one block at a time is widened, rotated, rounded and packed again.
+    constexpr bool kPacked = DT != I8F_F32 && !(HAD && ROT_F32);
     float v[kPacked ? 1 : VPT][8];
     uint4 raw[kPacked ? VPT : 1];
     if constexpr (kPacked) {
@@ -245,8 +259,45 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
         }
     }
 
-    if constexpr (HAD) {
-        constexpr float norm = (ROT_F32 || DT == I8F_F32) ? kNormF32 : kNormHalf;
+    if constexpr (HAD && kPacked) {
+        constexpr float norm = kNormHalf;
+        auto repack = [&](const float (&w)[8], uint4& dst) {   // (w * norm) rounded to DT, as packed pairs
+            dst.x = pack2<DT>(__fmul_rn(w[0], norm), __fmul_rn(w[1], norm));
+            dst.y = pack2<DT>(__fmul_rn(w[2], norm), __fmul_rn(w[3], norm));
+            dst.z = pack2<DT>(__fmul_rn(w[4], norm), __fmul_rn(w[5], norm));
+            dst.w = pack2<DT>(__fmul_rn(w[6], norm), __fmul_rn(w[7], norm));
+        };
+        if constexpr (kQuad) {
+#pragma unroll
+            for (int sgrp = 0; sgrp < VPT / 4; ++sgrp) {
+                float w[4][8];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) unpack8<DT>(raw[4 * sgrp + c], w[c]);
+                wht128_quad(w, lane);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) repack(w[c], raw[4 * sgrp + c]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                float w[8];
+                unpack8<DT>(raw[i], w);
+                wht128(w, lane);
+                repack(w, raw[i]);
+            }
+        }
+        if constexpr (MODE == kRowwise) {
+            if (xrot != nullptr && row_ok) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int vec = vec_of(i);
+                    if (vec < nvec)
+                        *reinterpret_cast<uint4*>(static_cast<unsigned short*>(xrot) + row * ldx + static_cast<int64_t>(vec) * 8) = raw[i];
+                }
+            }
+        }
+    } else if constexpr (HAD) {
+        constexpr float norm = kNormF32;   // fp32 rule: rotate in fp32, fp32 norm, no rounding (DT == fp32 or weights)
         if constexpr (kQuad) {
 #pragma unroll
             for (int sgrp = 0; sgrp < VPT / 4; ++sgrp) wht128_quad(*reinterpret_cast<float(*)[4][8]>(&v[4 * sgrp]), lane);
