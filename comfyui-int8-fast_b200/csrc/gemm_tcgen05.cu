@@ -918,7 +918,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
 template <int KIND>
 int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
                      const GemmParams& p, cudaStream_t st, const Scatter* scatter = nullptr) {
-    // I8F_GEMM_TILE = pair256 | s256 | s128 | s64 forces one tile configuration (experiments);
+    // I8F_GEMM_TILE = pair256 | s256 | s128 | s64 | s32 forces one tile configuration (experiments);
     // I8F_GEMM_SINGLE_CTA=1 is the older spelling of "never pair"
     static const int forced = [] {
         const char* e = getenv("I8F_GEMM_TILE");
@@ -927,13 +927,14 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
             if (e[0] == 's' && e[1] == '2') return 2;
             if (e[0] == 's' && e[1] == '1') return 3;
             if (e[0] == 's' && e[1] == '6') return 4;
+            if (e[0] == 's' && e[1] == '3') return 6;
         }
         const char* f = getenv("I8F_GEMM_SINGLE_CTA");
         return (f != nullptr && f[0] == '1') ? 5 : 0;
     }();
-    int choice;   // 1 pair 256 x 256, 2 single 128 x 256, 3 single 128 x 128, 4 single 128 x 64
-    if (forced >= 1 && forced <= 4) {
-        choice = forced;
+    int choice;   // 1 pair 256 x 256, 2 single 128 x 256, 3 single 128 x 128, 4 single 128 x 64, 5 single 128 x 32
+    if ((forced >= 1 && forced <= 4) || forced == 6) {
+        choice = forced == 6 ? 5 : forced;
     } else {
         // Problems that do not fill the GPU with 256-wide tiles are bound by how many SMs pull operands, not by the
         // tensor pipe (one tile's K loop costs 13 - 18 us whatever its width): take the configuration with the most
@@ -941,13 +942,15 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
         // runs the paired 256 x 256 tiles.  (Measured on M = 17 .. 2048, N = 4096 / 12288, K = 4096.)
         const int64_t sms = sm_count();
         const int64_t m128 = (M + 127) / 128, m256 = (M + 255) / 256;
-        const int64_t ctas[5] = {0, 2 * m256 * ((N + 255) / 256), m128 * ((N + 255) / 256), m128 * ((N + 127) / 128),
-                                 m128 * ((N + 63) / 64)};
-        const int64_t work[5] = {0, m256 * 256 * ((N + 255) / 256) * 256, m128 * 128 * ((N + 255) / 256) * 256,
-                                 m128 * 128 * ((N + 127) / 128) * 128, m128 * 128 * ((N + 63) / 64) * 64};
+        const int64_t ctas[6] = {0, 2 * m256 * ((N + 255) / 256), m128 * ((N + 255) / 256), m128 * ((N + 127) / 128),
+                                 m128 * ((N + 63) / 64), m128 * ((N + 31) / 32)};
+        const int64_t work[6] = {0, m256 * 256 * ((N + 255) / 256) * 256, m128 * 128 * ((N + 255) / 256) * 256,
+                                 m128 * 128 * ((N + 127) / 128) * 128, m128 * 128 * ((N + 63) / 64) * 64,
+                                 m128 * 128 * ((N + 31) / 32) * 32};
         choice = 0;
-        for (int c = 1; c <= 4; ++c) {
+        for (int c = 1; c <= 5; ++c) {
             if (c == 1 && forced == 5) continue;
+            if (c == 5 && scatter != nullptr) continue;   // the scatter epilogue stores 64-column pieces
             if (ctas[c] > sms) continue;
             if (choice == 0 || ctas[c] > ctas[choice] || (ctas[c] == ctas[choice] && work[c] < work[choice])) choice = c;
         }
@@ -957,6 +960,7 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
         case 1: return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st, scatter);
         case 2: return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
         case 3: return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
+        case 5: return launch_gemm<KIND, 32, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
         default: return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
     }
 }
