@@ -1,9 +1,13 @@
 // Library-wide entry points: version, error text, device check, status word.
+#include <atomic>
+
 #include "host_common.h"
 
 namespace i8f {
 
 static thread_local char t_error[512] = {0};
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 char* error_buffer() { return t_error; }
 
 // One status word per device; kernels receive its address as an argument.
@@ -28,6 +32,8 @@ int* device_status_word() {
 extern "C" {
 
 int i8f_version(void) { return I8F_VERSION; }
+
+uint64_t i8f_launch_count(void) { return i8f::g_launches.load(std::memory_order_relaxed); }
 
 const char* i8f_last_error(void) { return i8f::error_buffer(); }
 

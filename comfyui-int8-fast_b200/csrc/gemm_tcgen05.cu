@@ -1034,7 +1034,9 @@ static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, 
     p.epi_order = epilogue_order;
     p.add_existing = add_existing;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
-    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, static_cast<cudaStream_t>(stream), scatter);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    return launch_gemm_auto<kKindI8>(a, lda, w, ldw, M, N, K, p, st, scatter);
 }
 
 int i8f_linear_w8a8(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,

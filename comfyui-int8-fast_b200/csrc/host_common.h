@@ -31,9 +31,12 @@ inline int dtype_size(int dt) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+void count_launch();  // one more kernel launched by the library (defined in api.cu)
+
 inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    count_launch();
     return I8F_OK;
 }
 

@@ -56,6 +56,10 @@ extern "C" {
 /* Library version (I8F_VERSION of the build). */
 int i8f_version(void);
 
+/* Number of kernels this library has launched in the process so far (all devices, all streams); a host-side
+ * counter for accounting, e.g. launches per step = the difference around a step.  No counterpart in the reference. */
+uint64_t i8f_launch_count(void);
+
 /* Thread-local text of the last error returned on this thread ("" if none). */
 const char* i8f_last_error(void);
 
