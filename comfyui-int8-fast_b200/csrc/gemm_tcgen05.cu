@@ -12,7 +12,12 @@
 //                                    row per thread), dequantise / cast, store,
 //                                    then hand the TMEM buffer back (`acc_empty`)
 // The accumulator is double buffered in tensor memory (2 x BN columns) so the
-// epilogue of tile i overlaps the MMAs of tile i+1.
+// epilogue of tile i overlaps the MMAs of tile i+1.  The fused dynamic-LoRA
+// configuration (a third, fp32 accumulator for t @ lora_b^T next to the int32
+// ones) keeps 256-wide tiles with ONE int32 buffer instead and has eight
+// epilogue warps (two per 32-lane quarter, 320 threads) to keep the un-hidden
+// epilogue short.  16-bit outputs are computed as packed pairs and leave
+// through shared memory and TMA stores.
 //
 // PAIR variant (cta_group::2): two CTAs of a cluster work on one 256 x BN
 // tile.  Each loads its own 128 rows of A and its own BN/2 rows of B (half the
