@@ -471,3 +471,18 @@ def test_small_batch_linear_is_deterministic_and_checks_arguments(cuda_pkg):
         F.linear_small_batch(wl.activation(17, 512, seed=5).to(DEV), wq, ws, None)       # M > 16
     with pytest.raises(nat.NativeLibraryError):
         F.linear_small_batch(x[:, :40].contiguous(), wq[:, :40].contiguous(), ws, None)   # K % 16 != 0
+
+
+def test_launch_counter_counts_kernels(cuda_pkg):
+    """The library's own launch counter: a fused forward is two launches (quantise, GEMM), a tiny-batch call one."""
+    F, wl, nat = cuda_pkg.functional, cuda_pkg.workloads, cuda_pkg._native
+    lib = nat.load()
+    x = wl.activation(64, 256, seed=2).to(DEV)
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(96, 256, seed=2).numpy())
+    wq, ws = torch.from_numpy(wq).to(DEV), dev_ws(ws)
+    before = lib.i8f_launch_count()
+    F.linear_forward(x, wq, ws, None, torch.bfloat16)
+    assert lib.i8f_launch_count() - before == 2
+    before = lib.i8f_launch_count()
+    F.linear_small_batch(x[:4], wq, ws, None)
+    assert lib.i8f_launch_count() - before == 1
