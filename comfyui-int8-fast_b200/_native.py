@@ -68,6 +68,8 @@ _PROTOTYPES = {
                                 c_int64, c_void_p]),
     "i8f_lora_merge_sr": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int,
                                   c_int64, c_int64, c_int64, c_float, c_int, c_void_p, c_uint64, c_void_p]),
+    "i8f_lora_merge_max_rank": (c_int64, [c_int, c_int]),
+    "i8f_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, ctypes.c_uint32, c_int64, c_void_p]),
     "i8f_stochastic_round": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64,
                                      c_void_p, c_uint64, c_void_p]),
 }

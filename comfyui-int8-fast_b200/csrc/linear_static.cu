@@ -11,8 +11,12 @@
 // that allocates behind the scenes.
 //
 // Consequences the caller has to know (also stated in include/i8f.h):
-//   * Every GPU on which this library is loaded holds the array
-//     (I8F_STATIC_WORKSPACE_BYTES) from load until the process exits.
+//   * Every GPU that uses this entry point holds the array
+//     (I8F_STATIC_WORKSPACE_BYTES) until the process exits.  The driver backs
+//     it with device memory when this module is first touched on a device --
+//     with lazy module loading that is the first call here, which can
+//     therefore fail with I8F_ERR_CUDA on a GPU with nothing left; make it
+//     before the rest of the device is handed to a pool.
 //   * Problems whose workspace does not fit are refused with
 //     I8F_ERR_WORKSPACE; nothing is launched.
 //   * All calls on a device share the one array.  Calls that can overlap on
@@ -34,6 +38,8 @@ namespace {
 static __device__ __align__(256) unsigned char g_static_workspace[I8F_STATIC_WORKSPACE_BYTES];
 
 constexpr int kMaxDevices = 64;
+// Written without a lock: two host threads that race on a device's first call both look the address up and store
+// the same value, so the unsynchronised write is idempotent.
 unsigned char* s_workspace_addr[kMaxDevices] = {nullptr};
 
 // Device address of the array on the CURRENT device (looked up once per device).

@@ -389,12 +389,28 @@ stochastic_round_kernel(const float* __restrict__ delta, long long ldd, const fl
     }
 }
 
+// Shared memory of one CTA: the whole [r x 128] slice of `down` plus 32 rows of `up` (and, in the tensor-core
+// form, the fp32 accumulator tile).  This is what bounds the rank one launch can take.
+constexpr size_t kMergeSmemLimit = 200 * 1024;
+inline size_t merge_smem_bytes(bool tensor_path, int64_t r) {
+    const size_t r16 = static_cast<size_t>((r + 15) / 16 * 16);
+    return tensor_path ? static_cast<size_t>(kRowsPerIter) * kAccStride * sizeof(float) + static_cast<size_t>(128 + kRowsPerIter) * (r16 + 8) * 2
+                       : (static_cast<size_t>(r) * 128 + static_cast<size_t>(kRowsPerIter) * (r + 1)) * sizeof(float);
+}
+
 }  // namespace
 }  // namespace i8f
 
 using namespace i8f;
 
 extern "C" {
+
+int64_t i8f_lora_merge_max_rank(int factor_dtype, int with_uniforms) {
+    const bool tensor_path = factor_dtype != I8F_F32 && !with_uniforms;
+    int64_t r = 0;
+    while (merge_smem_bytes(tensor_path, r + 1) <= kMergeSmemLimit) ++r;
+    return r;
+}
 
 int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode, const void* up, int64_t ldup,
                       const void* down, int64_t lddown, int factor_dtype, int64_t N, int64_t K, int64_t r,
@@ -413,10 +429,10 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
     // supplies its own uniforms (the bit-exact parity mode), take the sequential fp32 kernel
     const bool tensor_path = factor_dtype != I8F_F32 && uniforms == nullptr && r > 0 && ldup % 2 == 0 && lddown % 2 == 0;
     const int r16 = static_cast<int>((r + 15) / 16 * 16);
-    const size_t smem = tensor_path
-        ? static_cast<size_t>(kRowsPerIter) * kAccStride * sizeof(float) + static_cast<size_t>(128 + kRowsPerIter) * (r16 + 8) * 2
-        : (static_cast<size_t>(r) * 128 + static_cast<size_t>(kRowsPerIter) * (r + 1)) * sizeof(float);
-    I8F_REQUIRE(smem <= 200 * 1024, I8F_ERR_UNSUPPORTED, "rank %lld too large for one pass", (long long)r);
+    const size_t smem = merge_smem_bytes(tensor_path, r);
+    I8F_REQUIRE(smem <= kMergeSmemLimit, I8F_ERR_UNSUPPORTED,
+                "rank %lld too large for one pass (limit %lld for this factor type; see i8f_lora_merge_max_rank)", (long long)r,
+                (long long)i8f_lora_merge_max_rank(factor_dtype, uniforms != nullptr ? 1 : 0));
     const int col_blocks = static_cast<int>((K + 127) / 128);
     // enough row bands to fill the GPU a few times over, each band a multiple of 32 rows
     int bands = (148 * 4 + col_blocks - 1) / col_blocks;

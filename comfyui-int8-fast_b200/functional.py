@@ -36,14 +36,26 @@ def _code(dtype: torch.dtype) -> int:
         raise TypeError(f"unsupported dtype {dtype}; expected bf16, fp16 or fp32") from None
 
 
-def _wscale_arg(w_scale, device: torch.device) -> tuple[Tensor, int]:
-    """Device fp32 tensor + granularity code from a float, 0-d/1-element tensor or [N,1]/[N] tensor."""
+def _wscale_arg(w_scale, device: torch.device, n_rows: int) -> tuple[Tensor, int]:
+    """Device fp32 tensor + granularity code from a float, 0-d/1-element tensor or [N,1]/[N] tensor.
+
+    A tensor scale must have exactly one entry or one per weight row: the C ABI cannot see the length, a shorter
+    vector would be read past its end by the kernel and a longer one (a block-wise scale, say) would be applied
+    with the wrong stride, where the reference's broadcast would raise.
+    """
     if not isinstance(w_scale, Tensor):
         return torch.tensor([float(w_scale)], dtype=torch.float32, device=device), nat.WSCALE_TENSOR
     ws = w_scale.to(device=device, dtype=torch.float32)
     if ws.numel() == 1:
         return ws.reshape(1), nat.WSCALE_TENSOR
+    if ws.numel() != n_rows:
+        raise ValueError(f"weight scale has {ws.numel()} entries; expected 1 or one per weight row ({n_rows})")
     return ws.reshape(-1).contiguous(), nat.WSCALE_CHANNEL
+
+
+def _check_weight(w: Tensor, K: int) -> None:
+    if w.dtype != torch.int8 or w.shape[1] != K:
+        raise ValueError(f"weight must be int8 [N, {K}], got {w.dtype} {tuple(w.shape)}")
 
 
 def quantize_rowwise(x: Tensor, hadamard: bool = False, return_rotated: bool = False):
@@ -121,9 +133,8 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
     q, w = _rows(q), _rows(w)
     M, K = q.shape
     N = w.shape[0]
-    ws, mode = _wscale_arg(w_scale, q.device)
-    if mode == nat.WSCALE_CHANNEL and ws.numel() != N:
-        raise ValueError(f"per-channel weight scale has {ws.numel()} entries for N={N}")
+    _check_weight(w, K)
+    ws, mode = _wscale_arg(w_scale, q.device, N)
     if bias is not None:
         bias = bias.to(q.device).contiguous()
     if add_into is not None:
@@ -148,7 +159,8 @@ def linear_w8a8_lora(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tenso
     M, K = q.shape
     N = w.shape[0]
     r = t.shape[1]
-    ws, mode = _wscale_arg(w_scale, q.device)
+    _check_weight(w, K)
+    ws, mode = _wscale_arg(w_scale, q.device, N)
     if bias is not None:
         bias = bias.to(q.device).contiguous()
     out = torch.empty((M, N), dtype=out_dtype, device=q.device)
@@ -170,7 +182,8 @@ def linear_w8a8_scatter(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Te
     q, w = _rows(q), _rows(w)
     M, K = q.shape
     N = w.shape[0]
-    ws, mode = _wscale_arg(w_scale, q.device)
+    _check_weight(w, K)
+    ws, mode = _wscale_arg(w_scale, q.device, N)
     if bias is not None:
         bias = bias.to(q.device).contiguous()
     arr = (ctypes.c_void_p * len(dest_ptrs))(*[ctypes.c_void_p(int(p)) for p in dest_ptrs])
@@ -187,7 +200,8 @@ def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype
     x, w = _rows(x), _rows(w)
     M, K = x.shape
     N = w.shape[0]
-    ws, mode = _wscale_arg(w_scale, x.device)
+    _check_weight(w, K)
+    ws, mode = _wscale_arg(w_scale, x.device, N)
     if bias is not None:
         bias = bias.to(x.device).contiguous()
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
@@ -211,7 +225,8 @@ def linear_small_batch(x: Tensor, w: Tensor, w_scale, bias: Tensor | None) -> Te
     x, w = _rows(x), _rows(w)
     M, K = x.shape
     N = w.shape[0]
-    ws, mode = _wscale_arg(w_scale, x.device)
+    _check_weight(w, K)
+    ws, mode = _wscale_arg(w_scale, x.device, N)
     if bias is not None:
         bias = bias.to(x.device).contiguous()
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
@@ -237,6 +252,7 @@ def linear_forward_static(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, ou
         raise ValueError("x and w must be 2-D with unit inner stride (this wrapper never copies)")
     M, K = x.shape
     N = w.shape[0]
+    _check_weight(w, K)
     if out.shape != (M, N) or out.stride(1) != 1:
         raise ValueError(f"out must be [{M},{N}] with unit inner stride")
     if not isinstance(w_scale, Tensor) or w_scale.device != x.device or w_scale.dtype != torch.float32:
@@ -312,11 +328,15 @@ def lora_merge_sr_(w: Tensor, w_scale, up: Tensor, down: Tensor, lora_scale: flo
     r = up.shape[1]
     if up.shape[0] != N or down.shape != (r, K):
         raise ValueError(f"factor shapes {tuple(up.shape)} x {tuple(down.shape)} do not give [{N},{K}]")
-    ws, mode = _wscale_arg(w_scale, w.device)
+    ws, mode = _wscale_arg(w_scale, w.device, N)
     if uniforms is not None:
         uniforms = uniforms.to(device=w.device, dtype=torch.float32).contiguous()
         if uniforms.shape != (N, K):
             raise ValueError("uniforms must have the shape of w")
+    limit = lora_merge_max_rank(up.dtype, uniforms is not None)
+    if r > limit:
+        raise ValueError(f"rank {r} exceeds the one-pass limit {limit} of the fused merge for {up.dtype} factors; "
+                         "build the delta and use stochastic_round instead")
     nat.check(nat.load().i8f_lora_merge_sr(nat.ptr(w), _ld(w), nat.ptr(ws), mode, nat.ptr(up), _ld(up), nat.ptr(down),
                                            _ld(down), _code(up.dtype), N, K, r, float(lora_scale), 1 if hadamard else 0,
                                            nat.ptr(uniforms), int(seed) & 0xFFFFFFFFFFFFFFFF,
@@ -324,12 +344,27 @@ def lora_merge_sr_(w: Tensor, w_scale, up: Tensor, down: Tensor, lora_scale: flo
     return w
 
 
+def lora_merge_max_rank(factor_dtype: torch.dtype, with_uniforms: bool = False) -> int:
+    """Largest rank the fused merge kernel takes in one launch for factors of this dtype."""
+    return int(nat.load().i8f_lora_merge_max_rank(_code(factor_dtype), 1 if with_uniforms else 0))
+
+
+def peer_barrier(flag_ptrs: list[int], rank: int, epoch: int, device: torch.device, limit_cycles: int = 2_000_000_000) -> None:
+    """Enqueue a meeting of the ranks on the current stream: publish `epoch` in every rank's flag array (raw device
+    pointers, this rank's own included), wait -- bounded -- until all ranks have published it in this rank's array."""
+    import ctypes
+    nat.require_device(device)
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*[ctypes.c_void_p(int(p)) for p in flag_ptrs])
+    nat.check(nat.load().i8f_peer_barrier(arr, len(flag_ptrs), rank, epoch & 0xFFFFFFFF, limit_cycles,
+                                          nat.current_stream(device)), "i8f_peer_barrier")
+
+
 def stochastic_round(delta: Tensor, w_scale, uniforms: Tensor | None = None, seed: int = 0) -> Tensor:
     """int8 = clamp(floor(delta/scale) + [u < frac]) for an fp32 [N,K] delta."""
     nat.require_device(delta.device)
     delta = _rows(delta.float())
     N, K = delta.shape
-    ws, mode = _wscale_arg(w_scale, delta.device)
+    ws, mode = _wscale_arg(w_scale, delta.device, N)
     out = torch.empty((N, K), dtype=torch.int8, device=delta.device)
     if uniforms is not None:
         uniforms = uniforms.to(device=delta.device, dtype=torch.float32).contiguous()

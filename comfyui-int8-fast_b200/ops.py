@@ -197,7 +197,15 @@ def _merge_int8(weight: Tensor, factors, delta, eff_scale, seed: int, comp_devic
     rotate = _quarot_enabled() and weight.shape[1] % quarot.GROUP_SIZE == 0
     if factors is not None:
         up, down, scale = factors
-        F.lora_merge_sr_(w, eff_scale, up.to(comp_device), down.to(comp_device), scale, hadamard=rotate, seed=seed)
+        up, down = up.to(comp_device), down.to(comp_device)
+        if up.shape[1] > F.lora_merge_max_rank(up.dtype):
+            # the fused kernel keeps a whole [rank x 128] slice of `down` in shared memory; a stack (or a single file)
+            # whose rank exceeds that takes the delta path below: the product in fp32, then ONE rounding, which is
+            # what the reference does for any number of LoRAs at any rank (int8_quant.py:355-404)
+            delta = torch.mm(up.float().flatten(1), down.float().flatten(1)) * scale
+            factors = None
+    if factors is not None:
+        F.lora_merge_sr_(w, eff_scale, up, down, scale, hadamard=rotate, seed=seed)
     else:
         d = delta.to(comp_device, torch.float32)
         if rotate:
@@ -322,6 +330,7 @@ class DynamicLoRAHook:
                 continue
             patches = per_layer.get(f"diffusion_model.{name}.weight") or per_layer.get(f"{name}.weight")
             module.lora_alpha = None
+            module._lora_cache = None      # converted copies of the factors belong to the tensors replaced below
             if not patches:
                 module.lora_A = module.lora_B = None
                 continue
@@ -349,14 +358,9 @@ class DynamicLoRAHook:
 # =============================================================================
 # Int8TensorwiseOps                                          int8_quant.py:522-792
 # =============================================================================
-@torch.compiler.disable
-def _prepare_lora(module, device: torch.device, dtype: torch.dtype):
-    """lora_A / lora_B in the compute dtype on `device`, rank padded to a multiple of 8 (16-byte rows
-    for the TMA loads); cached on the module until the tensors are replaced."""
-    key = (id(module.lora_A), id(module.lora_B), device, dtype, module.lora_alpha)
-    cache = getattr(module, "_lora_cache", None)
-    if cache is not None and cache[0] == key:
-        return cache[1], cache[2]
+def _convert_lora(module, device: torch.device, dtype: torch.dtype):
+    """lora_A / lora_B in the compute dtype on `device`, rank padded to a multiple of 8 (16-byte rows for the TMA
+    loads); plain tensor operations, so it also traces under torch.compile."""
     a = module.lora_A.to(device=device, dtype=dtype).flatten(1)
     b = module.lora_B.to(device=device, dtype=dtype).flatten(1)
     if module.lora_alpha is not None:
@@ -365,8 +369,23 @@ def _prepare_lora(module, device: torch.device, dtype: torch.dtype):
     if pad:
         a = torch.cat([a, a.new_zeros(pad, a.shape[1])], dim=0)
         b = torch.cat([b, b.new_zeros(b.shape[0], pad)], dim=1)
-    a, b = a.contiguous(), b.contiguous()
-    module._lora_cache = (key, a, b)
+    return a.contiguous(), b.contiguous()
+
+
+def _prepare_lora(module, device: torch.device, dtype: torch.dtype):
+    """The converted factors, cached on the module until the source tensors are replaced.  While a compiler traces
+    the forward the conversion is simply part of the graph (no cache: attribute writes would break the trace)."""
+    if torch.compiler.is_compiling():
+        return _convert_lora(module, device, dtype)
+    # The entry keeps the SOURCE tensors and is matched by identity: a key made of id() values alone could match a
+    # new pair of tensors that was allocated at the addresses of a freed pair (LoRA X -> none -> LoRA Y), and the
+    # layer would silently keep running X's converted factors.
+    key = (device, dtype, module.lora_alpha)
+    cache = getattr(module, "_lora_cache", None)
+    if cache is not None and cache[0] == key and cache[3] is module.lora_A and cache[4] is module.lora_B:
+        return cache[1], cache[2]
+    a, b = _convert_lora(module, device, dtype)
+    module._lora_cache = (key, a, b, module.lora_A, module.lora_B)
     return a, b
 
 
@@ -496,9 +515,10 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                 self._store("bias", out_bias, inplace_update)
 
             # ------------------------------------------------------------ forward
-            @torch.compiler.disable
             def _scale_on(self, device):
                 if self._weight_scale_scalar is not None:
+                    if torch.compiler.is_compiling():   # a constant of the traced graph; no attribute is written
+                        return torch.full((1,), self._weight_scale_scalar, dtype=torch.float32, device=device)
                     cached = self._scalar_scale_dev   # (value, device, 1-element fp32 tensor)
                     if cached is None or cached[0] != self._weight_scale_scalar or cached[1] != device:
                         t = torch.tensor([self._weight_scale_scalar], dtype=torch.float32, device=device)
@@ -506,23 +526,6 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     return cached[2]
                 ws = self.weight_scale
                 return ws if ws.device == device else ws.to(device, non_blocking=True)
-
-            @torch.compiler.disable
-            def _small_batch_forward(self, x2, weight, w_scale, bias, lora_in, has_lora, compute_dtype):
-                """M <= 16 tokens: activations stay unquantised and meet the dequantised weights (int8_quant.py:756-760);
-                the weights are dequantised inside the kernel, never materialised."""
-                with torch.cuda.device(x2.device):
-                    if self._use_quarot:
-                        lora_in = x2 = quarot.rotate_activation(x2, None, quarot.GROUP_SIZE)
-                    if x2.dtype in (torch.bfloat16, torch.float16) and x2.shape[1] % 16 == 0:
-                        y = F.linear_small_batch(x2, weight, w_scale, bias)
-                    else:   # fp32 activations or an odd K: the reference's expression as it stands
-                        w_float = dequantize(weight, w_scale.reshape(-1, 1) if w_scale.numel() > 1 else w_scale).to(x2.dtype)
-                        y = TF.linear(x2, w_float, bias.to(x2.dtype) if bias is not None else None)
-                    if has_lora:
-                        lora_a, lora_b = _prepare_lora(self, x2.device, compute_dtype)
-                        F.lora_up_add_(y, F.lora_down(lora_in, lora_a), lora_b)
-                return y
 
             def forward(self, x: Tensor) -> Tensor:
                 need_cast = self.comfy_cast_weights or len(self.weight_function) > 0 or len(self.bias_function) > 0
@@ -534,7 +537,8 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     uncast_bias_weight(self, weight, bias, stream)
                     return out
 
-                nat.require_device(x.device)
+                if not torch.compiler.is_compiling():   # the operators below check the device themselves when they run
+                    nat.require_device(x.device)
                 if need_cast:
                     weight, bias, stream = cast_bias_weight(self, input=None, dtype=torch.int8, device=x.device,
                                                             bias_dtype=x.dtype, offloadable=True)
@@ -547,7 +551,6 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     x2 = x2.to(compute_dtype)
                 rows = x2.shape[0]
                 has_lora = self.lora_A is not None and self.lora_B is not None
-                lora_in = x2
 
                 if rows > SMALL_BATCH_ROWS and has_lora:
                     # t = x @ A^T first; t @ B^T is accumulated inside the int8 GEMM kernel and added in its
@@ -560,7 +563,8 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                     y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
                                                   nat.EPI_PYTORCH)
                 else:
-                    y = self._small_batch_forward(x2, weight, w_scale, bias, lora_in, has_lora, compute_dtype)
+                    lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype) if has_lora else (None, None)
+                    y = custom_ops.small_batch_forward(x2, weight, w_scale, bias, lora_a, lora_b, self._use_quarot)
 
                 if need_cast:
                     uncast_bias_weight(self, weight, bias, stream)

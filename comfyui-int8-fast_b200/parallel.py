@@ -97,29 +97,68 @@ class FusedColumnParallelOutput:
     ranks' copies (TMA stores to this GPU's memory and, over NVLink, to the peers' mapped buffers), so there is
     no separate all-gather pass and the transfer overlaps the tensor-core main loop.  Only stores cross GPUs.
 
-    After `forward` returns, the local copy holds all columns once every rank's kernel has finished; `forward`
-    ends with a barrier over the symmetric-memory signal pads, stream-ordered on the current stream.
+    The ranks meet twice per `forward` in the library's own barrier kernel (`i8f_peer_barrier`): once before the
+    stores (nobody still reads the previous result) and once after them (every block has landed everywhere).
+    Its wait is BOUNDED: if a peer never arrives -- it raised on the host, it was killed -- the kernel gives up
+    after about a second and leaves code 105 in the device status word, which `check()` turns into an exception;
+    no rank is left spinning on the GPU.  Everything that can raise on one rank only (argument checks, the
+    activation quantiser) runs before the first meeting, and the width rule is evaluated for ALL ranks' blocks, so
+    the ranks either all pass it or all raise.
     """
+    WAIT_LIMIT_CYCLES = 4_000_000_000       # about two seconds of SM clocks
 
     def __init__(self, rows: int, out_features: int, dtype: torch.dtype, device: torch.device, group=None):
+        import os
+        # plain peer stores only: the buffers need no NVLink multicast binding
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
+        self.device = device
         self.out_features = out_features
+        widths = [e - b for b, e in (shard_bounds(out_features, self.world, r) for r in range(self.world))]
+        if any(w % 32 for w in widths):     # the same verdict on every rank
+            raise ValueError(f"the fused column-parallel path needs every rank's block width to be a multiple of 32, got {widths}")
         self.buffer = symm_mem.empty((rows, out_features), dtype=dtype, device=device)
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
         self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.flag_handle = symm_mem.rendezvous(self.flags, self.group)
+        dist.barrier(self.group)            # every rank's flags are zero before anyone publishes an epoch
+        torch.cuda.synchronize(device)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in self.flag_handle.buffer_ptrs]
         # own buffer first: the local store is the cheap one
         self.dest_ptrs = [self.peer_ptrs[self.rank]] + [p for r, p in enumerate(self.peer_ptrs) if r != self.rank]
+        self.epoch = 0
+
+    def _meet(self) -> None:
+        from . import functional as F
+        self.epoch += 1
+        F.peer_barrier(self.flag_ptrs, self.rank, self.epoch, self.device, self.WAIT_LIMIT_CYCLES)
 
     def forward(self, x: Tensor, shard: ColumnShard, hadamard: bool = False) -> Tensor:
         from . import functional as F
-        if (shard.end - shard.begin) % 32:
-            raise ValueError("the fused column-parallel path needs a block width that is a multiple of 32")
+        if shard.out_features != self.out_features or (shard.begin, shard.end) != shard_bounds(self.out_features, self.world, self.rank):
+            raise ValueError("the shard does not belong to this output buffer")
+        if x.shape[0] > self.buffer.shape[0]:
+            raise ValueError(f"{x.shape[0]} rows do not fit the buffer of {self.buffer.shape[0]}")
         q, xs = F.quantize_rowwise(x, hadamard=hadamard)
-        self.handle.barrier(channel=0)        # nobody still reads the previous step's result
+        self._meet()                          # nobody still reads the previous step's result
         F.linear_w8a8_scatter(q, xs, shard.weight, shard.weight_scale, shard.bias, self.dest_ptrs, self.out_features,
                               shard.begin, self.buffer.dtype)
-        self.handle.barrier(channel=1)        # every rank's block has landed everywhere
+        self._meet()                          # every rank's block has landed everywhere
         return self.buffer[: x.shape[0]]
+
+    def check(self) -> None:
+        """Synchronises the device and raises if a bounded wait of this library ran out since the last check (a peer
+        that did not arrive at a meeting, or a stalled pipeline inside a kernel)."""
+        from . import _native as nat
+        with torch.cuda.device(self.device):
+            status = nat.device_status()
+        if status != 0:
+            raise nat.NativeLibraryError(
+                f"device status {status}: a bounded device-side wait ran out"
+                + (" (a peer rank did not reach the column-parallel meeting point)" if status == 105 else ""))

@@ -165,6 +165,16 @@ int i8f_linear_w8a8_scatter(const int8_t* a, int64_t lda, const float* a_scale,
                             void* const* dests, int n_dests, int64_t ld_dest, int64_t n_total, int64_t col_offset,
                             int out_dtype, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
+/* Meeting point of the ranks of a column-parallel linear (one process per GPU), enqueued on `stream`.
+ * flag_arrays[p] is rank p's array of n_ranks 32-bit flags as mapped into THIS process (symmetric memory or
+ * CUDA IPC; zero before the first meeting).  The kernel publishes `epoch` in slot `rank` of every array with
+ * system-scope stores, then polls its OWN array until every slot has reached `epoch` (compared modulo 2^32, so
+ * epochs simply count up and flags are never cleared).  No load touches peer memory.  The wait gives up after
+ * `limit_cycles` SM clocks (2e9 is about a second) and records 105 in the device status word, so a rank that
+ * failed on the host costs its peers a bounded delay and an error, never a GPU that spins for ever.
+ * Ranks must not share a GPU.  n_ranks <= 8.  Has no counterpart in the reference, which is single-GPU. */
+int i8f_peer_barrier(void* const* flag_arrays, int n_ranks, int rank, uint32_t epoch, int64_t limit_cycles, void* stream);
+
 /* Bytes of caller-owned workspace i8f_linear_forward needs for an [M,K] input. */
 size_t i8f_linear_workspace_bytes(int64_t M, int64_t K);
 
@@ -188,10 +198,14 @@ int i8f_linear_forward(const void* x, int x_dtype, int64_t ldx, int hadamard128,
  * memory (a host that owns the whole device through its own pool, a loop that must stay off
  * the allocator, a sandbox that may only launch on a given stream).  Same arithmetic and
  * results as i8f_linear_forward; the int8 activations and their scales go to an array that is
- * part of the library image instead.  The call allocates nothing.
+ * part of the library image instead.  The call itself requests no memory (no cudaMalloc, no pool).
  *   - Limit: i8f_linear_workspace_bytes(M, K) <= I8F_STATIC_WORKSPACE_BYTES (e.g. M*K up to
  *     4096 x 4096); larger problems return I8F_ERR_WORKSPACE and launch nothing.
- *   - The array exists once per GPU that loaded the library and stays until the process exits.
+ *   - The array exists once per GPU that uses this entry point and stays until the process exits.
+ *     With CUDA's default lazy module loading the driver gives the array its device memory when the
+ *     module is first touched, which is the FIRST call of this function on a device: device memory in
+ *     use grows by the array's size during that call, and it can fail with I8F_ERR_CUDA if nothing is
+ *     left.  A host that hands the rest of the GPU to its own pool makes this first call before it does.
  *   - All calls share it: calls that may overlap on the GPU (different streams without an
  *     ordering between them) race.  It keeps the previous call's contents; no part of it
  *     needs to be zero on entry, every byte a call reads it has written first.
@@ -247,6 +261,15 @@ int i8f_lora_merge_sr(int8_t* w, int64_t ldw, const float* w_scale, int w_scale_
                       const void* up, int64_t ldup, const void* down, int64_t lddown, int factor_dtype,
                       int64_t N, int64_t K, int64_t r, float lora_scale, int hadamard128,
                       const float* uniforms, uint64_t seed, void* stream);
+
+/* Largest rank r one i8f_lora_merge_sr launch accepts for contiguous factors of `factor_dtype`
+ * (with_uniforms != 0: the call supplies its own uniforms).  A CTA keeps the whole [r x 128] slice of `down`
+ * in shared memory, which is what sets the limit: 319 for fp32 factors or supplied uniforms, 576 for 16-bit
+ * factors with the in-kernel counter RNG.  Callers with a larger (stacked) rank build the fp32 delta
+ * themselves and use i8f_stochastic_round, which has no rank in it.  The reference sums any number of
+ * deltas at any rank (int8_quant.py:355-404); the host layer of this package does the same on top of the
+ * two entry points. */
+int64_t i8f_lora_merge_max_rank(int factor_dtype, int with_uniforms);
 
 /* Stochastic rounding of an existing fp32 delta (same arithmetic as above
  * from `delta/ws` on), written to d8 without touching any weight.

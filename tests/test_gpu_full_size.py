@@ -1,0 +1,146 @@
+"""Parity at the benchmark's own sizes: the CUDA path against the CPU oracle on the same seeded inputs.
+
+The small-shape tests compare every bit against the NumPy bit-spec; here the shapes are the ones the
+benchmark times (the QuaRot MLP-up linear, the dynamic-LoRA linear and its stochastic merge, the linears of
+the synthetic DiT and of the column-parallel sweep).  The oracle side runs on the host: the canonical rotation
+and the quantisers from `oracle/bitspec.py` (NumPy), the exact int8 product through `torch._int_mm` on CPU
+tensors and the reference's epilogue expressions from `oracle/torch_path.py` (int8_quant.py:77-88, :107-119).
+Bars: int8 tensors, scales and int32 accumulators equal; 16-bit outputs equal for the plain linear (its
+epilogue is deterministic fp32) and within max|d| <= 1e-2 * RMS where a tensor-core fp32 sum is involved.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bitspec as bs
+from oracle import torch_path as tp
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+
+
+def _bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16)
+
+
+def _rms(t):
+    return float(t.double().pow(2).mean().sqrt())
+
+
+def _oracle_linear(x_bf16, wq, ws, bias, hadamard):
+    """(y, q, xs, acc) of the reference's CPU path with the canonical rotation in front."""
+    if hadamard:
+        x_bf16 = torch.from_numpy(bs.rotate_activation(x_bf16.float().numpy(), "bf16")).bfloat16()
+    return tp.linear_w8a8(x_bf16, wq, ws, bias, torch.bfloat16, hadamard=False, return_parts=True)
+
+
+def test_c1_quarot_mlp_up_full_size(cuda_pkg):
+    """Configuration 1 exactly as benchmarked: M=4096, K=4096, N=12288, weights rotated in fp32 and quantised with
+    one scale, activations rotated online, no bias, bf16 out.   quarot.py:42-102, int8_quant.py:23-26, :67-88"""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    shape = wl.CONFIGS["c1_quarot_mlp_up"]
+    M, K, N = shape.M, shape.K, shape.N
+    x = wl.activation(M, K, seed=0)
+    w = wl.weight_fp32(N, K, seed=0).bfloat16().float()        # the configuration's weights are bf16 values
+    wq_np, ws_np = bs.quantize_tensorwise(bs.rotate_weight(w.numpy()))
+    wq_d, ws_d = F.quantize_tensorwise(w.to(DEV), hadamard=True)
+    assert np.array_equal(wq_d.cpu().numpy(), wq_np), "rotated, tensorwise-quantised weights differ from the oracle"
+    assert np.float32(ws_d.item()) == np.float32(ws_np)
+    want, q_want, xs_want, acc_want = _oracle_linear(x, torch.from_numpy(wq_np), float(ws_np), None, True)
+
+    xd = x.to(DEV)
+    q, xs = F.quantize_rowwise(xd, hadamard=True)
+    assert torch.equal(q.cpu(), q_want), "int8 activations"
+    assert torch.equal(xs.cpu().reshape(-1), xs_want.reshape(-1)), "activation scales"
+    acc = F.gemm_i8_i32(q, wq_d)
+    assert torch.equal(acc.cpu(), acc_want), "int32 accumulators"
+    del acc
+    y = F.linear_forward(xd, wq_d, ws_d.reshape(1), None, torch.bfloat16, hadamard=True)
+    assert torch.equal(_bits(y), _bits(want)), "bf16 output of the fused forward"
+    assert cuda_pkg._native.device_status() == 0
+
+
+def test_c2_dynamic_lora_full_size(cuda_pkg):
+    """Configuration 2: M=8192, K=N=4096, per-channel weights, bias, rank-64 dynamic LoRA fused into the GEMM.
+    int8_quant.py:91-119, :763-774"""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    shape = wl.CONFIGS["c2_dynamic_lora"]
+    M, K, N, r = shape.M, shape.K, shape.N, shape.lora_rank
+    x = wl.activation(M, K, seed=0)
+    wq, ws = tp.quantize_rowwise(wl.weight_fp32(N, K, seed=0))
+    bias = wl.bias_fp32(N, seed=0)
+    lora_a, lora_b = wl.lora_factors(N, K, r, seed=0)
+    base, q_want, xs_want, acc_want = _oracle_linear(x, wq, ws, bias, False)
+    want = tp.lora_dynamic_add(base, x, lora_a, lora_b)
+
+    xd, wqd, wsd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), bias.to(DEV)
+    q, xs = F.quantize_rowwise(xd)
+    assert torch.equal(q.cpu(), q_want) and torch.equal(xs.cpu().reshape(-1), xs_want.reshape(-1))
+    assert torch.equal(F.gemm_i8_i32(q, wqd).cpu(), acc_want)
+    plain = F.linear_w8a8(q, xs, wqd, wsd, bd, torch.bfloat16)
+    assert torch.equal(_bits(plain), _bits(base)), "dequant + bias before the LoRA term"
+    t = F.lora_down(xd, lora_a.to(DEV))
+    y = F.linear_w8a8_lora(q, xs, wqd, wsd, bd, t, lora_b.to(DEV), torch.bfloat16).cpu()
+    err = (y.float() - want.float()).abs().max().item()
+    assert err <= TOL * _rms(want.float()), f"fused LoRA output off by {err}"
+    # the low-rank products run on tensor cores (fp32 partial sums in another order than the CPU library's), so a
+    # few outputs land one bf16 step away; anything more would be an error in the fused path
+    assert (_bits(y) != _bits(want)).float().mean().item() <= 0.02
+    assert cuda_pkg._native.device_status() == 0
+
+
+def test_c2_stochastic_merge_full_size(cuda_pkg):
+    """Configuration 2, second variant: rank-64 LoRA merged into int8 weights [4096, 4096].  With the uniforms
+    handed to both sides the result is equal; with the in-kernel Philox stream it is within the tensor-core bound
+    of the oracle fed the same stream.   int8_quant.py:36-62, :291-316"""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    N = K = 4096
+    r = 64
+    wq, ws = tp.quantize_rowwise(wl.weight_fp32(N, K, seed=0))
+    down, up = wl.lora_factors(N, K, r, seed=0)       # down = lora_A [r,K], up = lora_B [N,r]
+    u = wl.uniforms(N, K, seed=0)
+    want = bs.lora_merge(wq.numpy(), ws.numpy(), up.float().numpy(), down.float().numpy(), 1.0, u.numpy())
+    got = F.lora_merge_sr_(wq.to(DEV).clone(), ws.to(DEV), up.to(DEV), down.to(DEV), 1.0, uniforms=u.to(DEV))
+    assert np.array_equal(got.cpu().numpy(), want), "merge with shared uniforms"
+    # the same through the library expression of the reference (torch.mm orders the rank sum its own way)
+    lib = tp.lora_merge(wq, ws, up, down, 1.0, u).numpy()
+    assert (lib != want).mean() <= 1e-4
+
+    seed = 318008
+    want_p = bs.lora_merge(wq.numpy(), ws.numpy(), up.float().numpy(), down.float().numpy(), 1.0,
+                           bs.philox_uniforms(seed, N, K))
+    got_p = F.lora_merge_sr_(wq.to(DEV).clone(), ws.to(DEV), up.to(DEV), down.to(DEV), 1.0, seed=seed).cpu().numpy()
+    diff = got_p.astype(np.int32) - want_p.astype(np.int32)
+    assert np.abs(diff).max() <= 1 and (diff != 0).mean() <= 1e-4
+    assert (got_p != wq.numpy()).mean() > 0.05          # the merge did change the weights
+    assert cuda_pkg._native.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K,N,per_channel", [
+    (4608, 4096, 12288, False),      # DiT: qkv / MLP-up of a double block, one sample's 4096 + 512 tokens
+    (4608, 4096, 24576, False),      # DiT: fused qkv + MLP-up of a single block
+    (4608, 16384, 4096, False),      # DiT: fused attention-out + MLP-down of a single block
+    (4608, 12288, 4096, False),      # DiT: MLP-down of a double block
+    (4096, 4096, 16384, True),       # column-parallel sweep, unsharded
+])
+def test_dit_and_sweep_linears_full_size(cuda_pkg, M, K, N, per_channel):
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=3)
+    w = wl.weight_fp32(N, K, seed=3)
+    if per_channel:
+        wq, ws = tp.quantize_rowwise(w)
+    else:
+        wq, ws = tp.quantize_tensorwise(w)
+        ws = ws.reshape(1)
+    bias = wl.bias_fp32(N, seed=3).bfloat16()
+    want, q_want, xs_want, acc_want = _oracle_linear(x, wq, ws if per_channel else float(ws), bias, False)
+    xd, wqd = x.to(DEV), wq.to(DEV)
+    q, xs = F.quantize_rowwise(xd)
+    assert torch.equal(q.cpu(), q_want) and torch.equal(xs.cpu().reshape(-1), xs_want.reshape(-1))
+    acc = F.gemm_i8_i32(q, wqd)
+    assert torch.equal(acc.cpu(), acc_want), "int32 accumulators"
+    del acc
+    y = F.linear_forward(xd, wqd, ws.to(DEV), bias.to(DEV), torch.bfloat16)
+    assert torch.equal(_bits(y), _bits(want)), "bf16 output"
+    assert cuda_pkg._native.device_status() == 0

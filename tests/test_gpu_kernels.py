@@ -427,6 +427,33 @@ def test_bounded_wait_times_out_and_reports(cuda_pkg):
     assert bool((got == 64).all())
 
 
+def test_peer_barrier_meets_and_times_out_on_one_gpu(cuda_pkg):
+    """The column-parallel meeting kernel on ONE GPU, with the second rank played by the host: when the peer's slot
+    already holds the epoch the kernel passes at once and publishes its own slot in both arrays; when the peer never
+    arrives the wait gives up after its limit, the status word reads 105 and the context stays usable.  (Two ranks
+    that really wait on each other never share a GPU; the two-GPU form runs in the multi-GPU test.)"""
+    F, nat = cuda_pkg.functional, cuda_pkg._native
+    dev = torch.device(DEV)
+    mine = torch.zeros(8, dtype=torch.int32, device=DEV)      # rank 0's flag array
+    peer = torch.zeros(8, dtype=torch.int32, device=DEV)      # stands in for rank 1's (mapped) array
+    mine[1] = 5                                               # "rank 1 has reached epoch 5"
+    F.peer_barrier([mine.data_ptr(), peer.data_ptr()], 0, 5, dev, limit_cycles=200_000_000)
+    torch.cuda.synchronize()
+    assert nat.device_status() == 0
+    assert mine.tolist()[:2] == [5, 5] and peer.tolist()[:2] == [5, 0]
+    F.peer_barrier([mine.data_ptr(), peer.data_ptr()], 0, 4, dev, limit_cycles=200_000_000)   # an older epoch passes too
+    torch.cuda.synchronize()
+    assert nat.device_status() == 0
+    F.peer_barrier([mine.data_ptr(), peer.data_ptr()], 0, 6, dev, limit_cycles=20_000_000)    # nobody sets slot 1 to 6
+    torch.cuda.synchronize()
+    assert nat.device_status(reset=True) == 105
+    assert nat.device_status() == 0
+    assert bool((F.gemm_i8_i32(torch.ones(32, 64, dtype=torch.int8, device=DEV),
+                               torch.ones(16, 64, dtype=torch.int8, device=DEV)) == 64).all())
+    with pytest.raises(nat.NativeLibraryError):
+        F.peer_barrier([mine.data_ptr()] * 9, 0, 1, dev)
+
+
 # ------------------------------------------------------------------ tiny-batch branch (M <= 16)
 @pytest.mark.parametrize("M,K,N,per_channel,bias_dt,dt", [
     (1, 4096, 4096, False, torch.bfloat16, torch.bfloat16),     # a modulation-sized call

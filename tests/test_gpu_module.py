@@ -206,6 +206,62 @@ def test_patch_adapters_merge_in_int8_space(cuda_pkg, ops):
     assert np.array_equal(got.numpy(), bs.lora_merge(wq, ws, cat_up, cat_down, 1.0, u))
 
 
+def test_stack_whose_ranks_exceed_the_fused_kernel_takes_the_delta_path(cuda_pkg, ops):
+    """Five rank-64 + one rank-16 LoRAs (fp32 after the adapter's cast: 336 > the 319 the fused merge kernel holds
+    in shared memory) still merge with ONE rounding, as the reference does for any stack (int8_quant.py:355-404)."""
+    o, F, wl = cuda_pkg.ops, cuda_pkg.functional, cuda_pkg.workloads
+    N, K = 160, 256
+    assert F.lora_merge_max_rank(torch.float32) == 319 and F.lora_merge_max_rank(torch.bfloat16) == 576
+    assert F.lora_merge_max_rank(torch.bfloat16, with_uniforms=True) == 319
+    wq, ws = bs.quantize_rowwise(wl.weight_fp32(N, K, seed=11).numpy())
+    base = type("A", (), {})
+    patches, ups, downs = [], [], []
+    for i, r in enumerate([64, 64, 64, 64, 64, 16]):
+        down, up = wl.lora_factors(N, K, r, seed=20 + i)
+        up = (up.float() * 10).bfloat16()
+        a = base()
+        a.loaded_keys, a.weights = {"k"}, (up, down, None, None, None, None)
+        strength = 0.5 + 0.25 * i
+        patches.append((a, strength))
+        ups.append(to_np(up) * np.float32(strength))
+        downs.append(to_np(down))
+    merged = o.INT8MergedLoRAPatchAdapter(patches, torch.from_numpy(ws), seed=99)
+    got = merged.calculate_weight(torch.from_numpy(wq), "k", 1.0, 1.0, None, None).numpy()
+    delta = np.concatenate(ups, axis=1).astype(np.float64) @ np.concatenate(downs, axis=0).astype(np.float64)
+    want = np.clip(wq.astype(np.int32) + bs.stochastic_round(delta.astype(np.float32), ws, bs.philox_uniforms(99, N, K)), -128, 127)
+    diff = got.astype(np.int32) - want
+    assert np.abs(diff).max() <= 1 and (diff != 0).mean() <= 2e-3     # library fp32 product vs float64 in the delta
+    assert (got != wq).mean() > 0.2
+    # a single fp32 LoRA file above the limit goes the same way
+    down, up = wl.lora_factors(N, K, 336, seed=40, dtype=torch.float32)
+    ad = o.INT8LoRAPatchAdapter({"k"}, (up, down, None, None, None, None), torch.from_numpy(ws), seed=99)
+    got1 = ad.calculate_weight(torch.from_numpy(wq), "k", 1.0, 1.0, None, None).numpy()
+    d1 = up.double().numpy() @ down.double().numpy()
+    want1 = np.clip(wq.astype(np.int32) + bs.stochastic_round(d1.astype(np.float32), ws, bs.philox_uniforms(99, N, K)), -128, 127)
+    assert (got1 != want1).mean() <= 2e-3
+    with pytest.raises(ValueError, match="one-pass limit"):
+        F.lora_merge_sr_(torch.from_numpy(wq).to(DEV), torch.from_numpy(ws).to(DEV), up.to(DEV), down.to(DEV), 1.0)
+
+
+def test_wrong_length_weight_scale_is_refused(cuda_pkg):
+    """A per-channel scale with another length than N (a block-wise scale, a slice that was not narrowed) raises on
+    the host instead of being read past its end or applied with the wrong stride by a kernel."""
+    F = cuda_pkg.functional
+    x = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(48, 64, dtype=torch.int8, device=DEV)
+    for bad in (torch.ones(47, device=DEV), torch.ones(48, 2, device=DEV)):
+        with pytest.raises(ValueError, match="weight scale"):
+            F.linear_forward(x, w, bad, None, torch.bfloat16)
+        with pytest.raises(ValueError, match="weight scale"):
+            F.linear_small_batch(x[:4], w, bad, None)
+        with pytest.raises(ValueError, match="weight scale"):
+            F.stochastic_round(torch.zeros(48, 64, device=DEV), bad)
+    with pytest.raises(ValueError, match="int8"):
+        F.linear_forward(x, w.float(), torch.ones(1, device=DEV), None, torch.bfloat16)
+    with pytest.raises(ValueError, match="int8"):
+        F.linear_forward(x, w[:, :32], torch.ones(1, device=DEV), None, torch.bfloat16)
+
+
 def test_set_weight_requantises_float_results(cuda_pkg, ops):
     wl = cuda_pkg.workloads
     N, K = 64, 128
@@ -261,3 +317,83 @@ def test_linear_traces_under_torch_compile(cuda_pkg, ops):
     want = lin(x)
     dynamo.reset()
     assert torch.equal(torch.compile(lin, backend="eager")(x), want)
+
+
+class _TwoLayer(torch.nn.Module):
+    def __init__(self, l1, l2):
+        super().__init__()
+        self.l1, self.l2 = l1, l2
+
+    def forward(self, x):
+        return self.l2(torch.nn.functional.gelu(self.l1(x), approximate="tanh"))
+
+
+@pytest.mark.parametrize("with_lora", [False, True])
+def test_two_layer_mlp_compiles_without_graph_breaks(cuda_pkg, ops, with_lora):
+    """A small MLP of Int8 Linears under torch.compile(fullgraph=True) with the default backend: one graph, no break
+    at the custom operators, same bits as eager.  The node pack's fast mode is the compiled model (its README);
+    the kernels stay the hand-written ones, the compiler only generates the glue between them."""
+    wl = cuda_pkg.workloads
+    K, H, M = 256, 384, 64
+    layers = []
+    for i, (k, n) in enumerate(((K, H), (H, K))):
+        wq, ws = bs.quantize_rowwise(wl.weight_fp32(n, k, seed=30 + i).numpy())
+        lin = make_linear(ops, {"weight": torch.from_numpy(wq), "weight_scale": torch.from_numpy(ws),
+                                "bias": wl.bias_fp32(n, seed=30 + i).bfloat16()}, k, n)
+        if with_lora:
+            a, b = wl.lora_factors(n, k, 8, seed=30 + i)
+            lin.lora_A, lin.lora_B = a.to(DEV), b.to(DEV)
+        layers.append(lin)
+    model = _TwoLayer(*layers)
+    x = wl.activation(M, K, seed=31).to(DEV)
+    want = model(x)
+    from torch import _dynamo as dynamo
+    dynamo.reset()
+    try:
+        compiled = torch.compile(model, fullgraph=True)
+        got = compiled(x)
+    except Exception as e:  # noqa: BLE001 - a graph break raises under fullgraph=True; a missing host compiler does too
+        if "fullgraph" in repr(e) or "graph break" in repr(e).lower() or "Unsupported" in type(e).__name__:
+            raise
+        pytest.skip(f"the default compile backend is not usable on this box: {e!r:.200}")
+    # the GELU between the layers is generated code: its bf16 result may differ in the last place from eager
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * want.float().pow(2).mean().sqrt().item()
+    explain = dynamo.explain(model)(x)
+    assert explain.graph_count == 1 and explain.graph_break_count == 0
+    dynamo.reset()
+
+
+def test_cuda_graph_replay_of_the_dit_step_equals_eager(cuda_pkg):
+    """The toy DiT captured into a CUDA graph and replayed twice gives the eager result bit for bit (every int8
+    layer launches through the C ABI on the capturing stream; nothing allocates outside torch's graph pool)."""
+    import importlib
+    dit = importlib.import_module(cuda_pkg.__name__ + ".dit")
+    cfg = dit.DiTConfig(hidden=256, heads=2, mlp_ratio=3, double_blocks=1, single_blocks=2, img_tokens=64, txt_tokens=32,
+                        in_channels=16, txt_dim=128)
+    model = dit.SyntheticDiT(cfg, seed=3, device=DEV)
+    gen = torch.Generator().manual_seed(0)
+    img = torch.randn(1, cfg.img_tokens, cfg.in_channels, generator=gen).bfloat16().to(DEV)
+    txt = torch.randn(1, cfg.txt_tokens, cfg.txt_dim, generator=gen).bfloat16().to(DEV)
+    t = torch.full((1,), 0.5, device=DEV)
+    want = model(img, txt, t).clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            model(img, txt, t)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model(img, txt, t)
+    for _ in range(2):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    # new inputs in the captured buffers: the replay follows them
+    img.copy_(torch.randn(1, cfg.img_tokens, cfg.in_channels, generator=gen).bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, model(img, txt, t))
+    assert cuda_pkg._native.device_status() == 0

@@ -316,3 +316,46 @@ def test_custom_ops_have_shape_functions(pkg):
         b = torch.empty(24, 8, dtype=torch.bfloat16, device="cuda")
         y2 = torch.ops.int8_fast_b200.linear_lora_forward(x, w, ws, None, a, b, torch.float16, False, True, 0)
         assert y2.shape == (40, 24) and y2.dtype == torch.float16
+        y3 = torch.ops.int8_fast_b200.small_batch_forward(x[:4], w, ws, None, a, b, False)
+        assert y3.shape == (4, 24) and y3.dtype == torch.bfloat16
+
+
+def test_lora_cache_follows_the_source_tensors(pkg):
+    """LoRA X -> none -> LoRA Y with factors in a non-compute dtype (so converted copies exist): the converted
+    factors must be Y's, also when Y's tensors sit where X's were.  The cache entry holds the source tensors and is
+    matched by identity, and the hook drops it whenever it replaces them."""
+    o = pkg.ops
+    mod = types.SimpleNamespace(lora_A=None, lora_B=None, lora_alpha=None, _lora_cache=None)
+    cpu = torch.device("cpu")
+    xa, xb = torch.full((4, 16), 1.0, dtype=torch.float16), torch.full((8, 4), 2.0, dtype=torch.float16)
+    mod.lora_A, mod.lora_B = xa, xb
+    a1, b1 = o._prepare_lora(mod, cpu, torch.bfloat16)
+    assert a1.dtype == torch.bfloat16 and a1.shape == (8, 16) and b1.shape == (8, 8)      # rank padded to 8
+    assert o._prepare_lora(mod, cpu, torch.bfloat16)[0] is a1                              # cached while unchanged
+    mod.lora_A = mod.lora_B = None
+    ya, yb = torch.full((4, 16), 3.0, dtype=torch.float16), torch.full((8, 4), 4.0, dtype=torch.float16)
+    mod.lora_A, mod.lora_B = ya, yb
+    # the worst case: an id()-keyed cache entry that happens to match the new tensors' addresses
+    mod._lora_cache = ((cpu, torch.bfloat16, None), a1, b1, xa, xb)
+    a2, b2 = o._prepare_lora(mod, cpu, torch.bfloat16)
+    assert float(a2[0, 0]) == 3.0 and float(b2[0, 0]) == 4.0
+    # in-place edits of the same tensors keep the entry (the reference re-reads the tensors each call; the hook
+    # always assigns new ones, int8_quant.py:476-496)
+    hook = o.DynamicLoRAHook()
+    layer = nn.Linear(16, 8)
+    layer.lora_A, layer.lora_B, layer.lora_alpha, layer._lora_cache = xa, xb, None, ("stale",)
+    model = nn.Sequential(layer)
+    hook.apply_composition(model, [])
+    assert layer.lora_A is None and layer._lora_cache is None
+
+
+def test_weight_scale_length_is_checked_on_the_host(pkg):
+    F = pkg.functional
+    cpu = torch.device("cpu")
+    ws, mode = F._wscale_arg(torch.ones(7, 1), cpu, 7)
+    assert mode == pkg._native.WSCALE_CHANNEL and ws.shape == (7,)
+    assert F._wscale_arg(0.5, cpu, 7)[1] == pkg._native.WSCALE_TENSOR
+    assert F._wscale_arg(torch.tensor(0.5), cpu, 7)[1] == pkg._native.WSCALE_TENSOR
+    for bad in (torch.ones(6), torch.ones(7, 2), torch.ones(14)):
+        with pytest.raises(ValueError, match="weight scale"):
+            F._wscale_arg(bad, cpu, 7)
