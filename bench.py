@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the W8A8 linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2|c2merge|c4|dit|smallm] [--impl reference]
 
 One "step" is one pass of the hot path over one batch of synthetic input:
 (Hadamard rotation +) per-token int8 quantisation, the int8 tensor-core GEMM
@@ -11,9 +11,19 @@ N > 1 every rank runs its own batch of tokens against replicated weights
 (token-parallel, no data-path collective), so scaling is weak.
 
 Prints ONE JSON line (rank 0).  `value` is aggregate int8 tensor throughput
-with inputs resident in HBM; `e2e` is the same metric through the public
-module call with host buffers (pinned host -> device copy of the activations
-and device -> host copy of the output inside the timed region).
+with inputs resident in HBM, every timed step going through the public fused
+call; `roofline` times the GEMM (and the quantiser) alone in a loop of their
+own; `e2e` is the same metric through the ops-class module call with host
+buffers (pinned host -> device copy of the activations and device -> host copy
+of the output inside the timed region), next to the same copies without
+kernels.  The default workload also carries, measured in the same process
+outside the headline region:
+    parity       the timed inputs checked against the CPU oracle
+    comparators  torch._int_mm and the library expression of the step on this GPU
+    sustained    the step back to back for seconds (power-managed steady state)
+    dit          the synthetic 9B-class DiT denoising step (one sample per GPU)
+    c4           (N > 1) the column-parallel sweep: fused epilogue scatter vs NCCL
+                 all-gather, with equality checks the run fails on
 """
 from __future__ import annotations
 
@@ -133,6 +143,8 @@ def build_cpu_inputs(shape, seed: int, rows: int | None = None):
     M = shape.M if rows is None else rows
     x = wl.activation(M, shape.K, seed=seed)
     w = wl.weight_fp32(shape.N, shape.K, seed=seed)
+    if shape.hadamard:
+        w = w.bfloat16().float()          # the QuaRot configuration starts from bf16 weights
     b = wl.bias_fp32(shape.N, seed=seed) if shape.bias else None
     lora = wl.lora_factors(shape.N, shape.K, shape.lora_rank, seed=seed) if shape.lora_rank else None
     return x, w, b, lora
@@ -200,10 +212,9 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------- GPU arm
-def run_gpu_arm(args):
+def rank_context():
+    """(rank, world, local_rank, device, dist-or-None); initialises NCCL when launched with more than one rank."""
     import torch
-    import __graft_entry__ as g
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -214,14 +225,166 @@ def run_gpu_arm(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+    return rank, world, local_rank, dev, dist
 
+
+def make_sync(dist):
+    import torch
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+    return sync_all
+
+
+def max_over_ranks(values, dev, dist):
+    import torch
+    if dist is None:
+        return [float(v) for v in values]
+    t = torch.tensor(list(values), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def make_module(pkg, s, shape):
+    """The public layer object a user of the node pack holds: an ops-class Linear loaded from a pre-quantised
+    state dict (int8 weight + weight_scale [+ bias]), QuaRot flag and dynamic-LoRA factors set as the loader /
+    the hook would set them."""
+    lin = pkg.ops.StandaloneInt8Ops.Linear(shape.K, shape.N, bias=shape.bias, device="meta")
+    sd = {"weight": s["wq"], "weight_scale": s["ws"].reshape(-1, 1) if shape.per_channel else s["ws"].reshape(1).clone()}
+    if shape.bias:
+        sd["bias"] = s["bias"]
+    lin._load_from_state_dict(sd, "", {}, True, [], [], [])
+    lin._use_quarot = shape.hadamard
+    if s["lora"] is not None:
+        lin.lora_A, lin.lora_B = s["lora"]
+    return lin
+
+
+def parity_record(pkg, shape, s, dev):
+    """The timed configuration's first buffer set against the CPU oracle: int8 activations, scales and int32
+    accumulators must be equal, the 16-bit output is compared bit for bit and as max|d| / RMS.  The oracle is the
+    checker here, nothing of it is timed.  The rotation on the oracle side is the canonical butterfly of
+    oracle/bitspec.py (the reference's own library matmul orders its fp32 sums backend by backend)."""
+    import torch
+    from oracle import bitspec as bs
+    from oracle import torch_path as tp
+    F = pkg.functional
+    t0 = time.perf_counter()
+    x = s["x"].cpu()
+    wq, ws = s["wq"].cpu(), s["ws"].cpu()
+    bias = None if s["bias"] is None else s["bias"].cpu()
+    xr = torch.from_numpy(bs.rotate_activation(x.float().numpy(), "bf16")).bfloat16() if shape.hadamard else x
+    want, q_want, xs_want, acc_want = tp.linear_w8a8(xr, wq, ws.reshape(-1, 1) if shape.per_channel else float(ws.reshape(-1)[0]),
+                                                     bias, torch.bfloat16, hadamard=False, return_parts=True)
+    q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
+    acc = F.gemm_i8_i32(q, s["wq"])
+    y = F.linear_forward(s["x"], s["wq"], s["ws"], s["bias"], torch.bfloat16, hadamard=shape.hadamard)
+    rec = {"against": "oracle/torch_path.py (CPU, canonical rotation from oracle/bitspec.py)", "buffer_set": 0,
+           "int8_activations_equal": bool(torch.equal(q.cpu(), q_want)),
+           "activation_scales_equal": bool(torch.equal(xs.cpu().reshape(-1), xs_want.reshape(-1))),
+           "int32_accumulators_equal": bool(torch.equal(acc.cpu(), acc_want))}
+    del acc
+    yc = y.cpu()
+    if s["lora"] is not None:
+        want = tp.lora_dynamic_add(want, xr, s["lora"][0].cpu(), s["lora"][1].cpu())
+        yc = pkg.custom_ops.linear_lora_forward(s["x"], s["wq"], s["ws"], s["bias"], s["lora"][0], s["lora"][1], torch.bfloat16,
+                                                shape.hadamard, False, 0).cpu()
+    rms = float(want.double().pow(2).mean().sqrt())
+    rec["out_bits_equal"] = bool(torch.equal(yc.view(torch.int16), want.view(torch.int16)))
+    rec["out_max_abs_err_over_rms"] = float((yc.double() - want.double()).abs().max()) / rms
+    rec["out_tolerance"] = 1e-2
+    rec["ok"] = bool(rec["int8_activations_equal"] and rec["activation_scales_equal"] and rec["int32_accumulators_equal"]
+                     and rec["out_max_abs_err_over_rms"] <= 1e-2)
+    rec["seconds"] = round(time.perf_counter() - t0, 2)
+    return rec
+
+
+def comparators_record(shape, sets, steps: int):
+    """The kernels to beat on the same GPU, on the same tensors: the library int8 GEMM (torch._int_mm, cuBLASLt) alone,
+    and the whole step as the reference's non-Triton CUDA path expresses it with library kernels
+    (rotate_activation quarot.py:73-102 -> quantize_int8_axiswise int8_quant.py:28-31 -> torch._int_mm :80 ->
+    scale and cast :84 / :115 -> bias :86-87).  Not the product path; timed for comparison only."""
+    import torch
+    M, K, N = shape.M, shape.K, shape.N
+    dev = sets[0]["x"].device
+    h128 = None
+    if shape.hadamard:
+        idx = torch.arange(128, device=dev)
+        bits = idx[:, None] & idx[None, :]
+        par = torch.zeros_like(bits)
+        for b in range(7):
+            par ^= (bits >> b) & 1
+        h128 = ((1 - 2 * par).float() / (128 ** 0.5)).to(torch.bfloat16)
+
+    def library_step(s):
+        x = s["x"]
+        if h128 is not None:
+            x = torch.matmul(x.view(M, K // 128, 128), h128).view(M, K)
+        absmax = x.abs().amax(dim=-1, keepdim=True)
+        xs = (absmax.float() / 127.0).clamp(min=1e-30)
+        q = x.float().mul(1.0 / xs).round_().clamp_(-128.0, 127.0).to(torch.int8)
+        acc = torch._int_mm(q, s["wq"].T)
+        if shape.per_channel:
+            y = acc.float().mul_(xs).mul_(s["ws"].reshape(1, -1)).to(torch.bfloat16)
+        else:
+            y = acc.float().mul_(s["ws"].reshape(()) * xs).to(torch.bfloat16)
+        if s["bias"] is not None:
+            y = y + s["bias"].to(torch.bfloat16)
+        return q, y
+
+    n = len(sets)
+    qs = [library_step(s)[0] for s in sets]
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for i in range(3):
+        torch._int_mm(qs[i % n], sets[i % n]["wq"].T)
+    torch.cuda.synchronize()
+    for i, (a, b) in enumerate(ev):
+        a.record()
+        torch._int_mm(qs[i % n], sets[i % n]["wq"].T)
+        b.record()
+    torch.cuda.synchronize()
+    mm = sorted(a.elapsed_time(b) for a, b in ev[1:])
+    for i in range(2):
+        library_step(sets[i % n])
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        library_step(sets[i % n])
+    b.record()
+    torch.cuda.synchronize()
+    lib_ms = a.elapsed_time(b) / steps
+    ops = 2.0 * M * N * K
+    return {"int_mm_ms_median": median(mm), "int_mm_ms_best": mm[0], "int_mm_tops": ops / (median(mm) * 1e-3) / 1e12,
+            "int_mm_output": "int32 [M,N] (no epilogue)", "library_step_ms": lib_ms,
+            "library_step_tops": ops / (lib_ms * 1e-3) / 1e12, "n": steps,
+            "what": "torch._int_mm alone; and rotate -> quantise -> _int_mm -> scale -> bf16 (+bias) with library "
+                    "kernels, the reference's CUDA path without Triton (its Triton kernels are not on this box)"}
+
+
+def run_gpu_arm(args):
+    import torch
+    import __graft_entry__ as g
+
+    rank, world, local_rank, dev, dist = rank_context()
+    sync_all = make_sync(dist)
     pkg = g.load_package()
     F, nat = pkg.functional, pkg._native
     nat.require_device(dev)
     shape = workload_shape(args.workload)
     M, K, N = shape.M, shape.K, shape.N
     out_dtype = torch.bfloat16
+    extras = args.workload == "c1" and not args.headline_only
 
     # Weak scaling: rank r owns its own batch of M tokens (seed differs per rank), weights replicated.
     sets = []
@@ -238,46 +401,20 @@ def run_gpu_arm(args):
                      "bias": None if b is None else b.to(dev).to(out_dtype),
                      "lora": None if lora is None else (lora[0].to(dev), lora[1].to(dev)),
                      "y_host": torch.empty((M, N), dtype=out_dtype).pin_memory()})
-    gemm_events = []
-
     workspace = torch.empty((nat.load().i8f_linear_workspace_bytes(M, K),), dtype=torch.uint8, device=dev)
-    EVENT_EVERY = 8   # the GEMM launch is bracketed by CUDA events on every 8th step of the timed region
 
-    def step(i: int, timed: bool):
+    def step(i: int):
+        """One pass of the hot path through the public fused call: K1 and K2 back to back on the stream."""
         s = sets[i % N_BUFFER_SETS]
-        if s["lora"] is None and not (timed and i % EVENT_EVERY == 0):
-            # the public fused call: K1 and K2 back to back on the stream (programmatic dependent launch), no events
+        if s["lora"] is None:
             return F.linear_forward(s["x"], s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard,
                                     workspace=workspace)
-        if s["lora"] is not None and not (timed and i % EVENT_EVERY == 0):
-            # the public fused-LoRA op: K1 and the LoRA down projection overlap on two streams, then the fused GEMM
-            return pkg.custom_ops.linear_lora_forward(s["x"], s["wq"], s["ws"], s["bias"], s["lora"][0], s["lora"][1], out_dtype,
-                                                      shape.hadamard, False, nat.EPI_PYTORCH)
-        timed = timed and i % EVENT_EVERY == 0
-        q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
-        # dynamic LoRA: t = x @ A^T, then the int8 GEMM accumulates t @ B^T in a second tensor-memory accumulator
-        lora_t = F.lora_down(s["x"], s["lora"][0]) if s["lora"] is not None else None
-        if timed:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        if lora_t is not None:
-            y = F.linear_w8a8_lora(q, xs, s["wq"], s["ws"], s["bias"], lora_t, s["lora"][1], out_dtype)
-        else:
-            y = F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype)
-        if timed:
-            e1.record()
-            gemm_events.append((e0, e1))
-        return y
+        return pkg.custom_ops.linear_lora_forward(s["x"], s["wq"], s["ws"], s["bias"], s["lora"][0], s["lora"][1], out_dtype,
+                                                  shape.hadamard, False, nat.EPI_PYTORCH)
 
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-
+    # ---- headline: W warm-up steps, then exactly K timed steps between barriers, max over ranks
     for i in range(args.warmup):
-        step(i, False)
+        step(i)
     sync_all()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -289,30 +426,61 @@ def run_gpu_arm(args):
     launches_before = nat.load().i8f_launch_count()
     t_start.record()
     for i in range(args.steps):
-        step(i, True)
+        step(i)
     t_end.record()
     launches_timed = nat.load().i8f_launch_count() - launches_before   # counted by the library itself
     sync_all()
     host_t1 = time.perf_counter()
     elapsed_ms = t_start.elapsed_time(t_end)
     clocks = sampler.stop(host_t0, host_t1) if sampler else None
-    gemm_ms = sorted(a.elapsed_time(b) for a, b in gemm_events)
-    gemm_avg_ms = sum(gemm_ms) / len(gemm_ms)
 
-    # end-to-end: host buffers through the public forward call, copies inside the timed region.  The three phases of
-    # consecutive steps overlap as a serving loop would run them: host->device copy on one stream, the forward on the
-    # current stream, device->host copy of the result on a third (PCIe is full duplex); every step still moves its own
-    # input and its own output.
+    # ---- the two kernels on their own: KERNEL_SAMPLES event-bracketed launches each, back to back over the rotating
+    # buffer sets (so operands come from HBM, not L2); the first launch after the idle gap is discarded
+    KERNEL_SAMPLES = 33
+    quantised = [F.quantize_rowwise(s["x"], hadamard=shape.hadamard) for s in sets]
+    lora_ts = [F.lora_down(s["x"], s["lora"][0]) if s["lora"] is not None else None for s in sets]
+
+    def gemm_only(i):
+        s, (q, xs) = sets[i % N_BUFFER_SETS], quantised[i % N_BUFFER_SETS]
+        if s["lora"] is not None:
+            return F.linear_w8a8_lora(q, xs, s["wq"], s["ws"], s["bias"], lora_ts[i % N_BUFFER_SETS], s["lora"][1], out_dtype)
+        return F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], out_dtype)
+
+    def quant_only(i):
+        return F.quantize_rowwise(sets[i % N_BUFFER_SETS]["x"], hadamard=shape.hadamard)
+
+    def bracketed(fn):
+        for i in range(4):
+            fn(i)
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(KERNEL_SAMPLES)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            fn(i)
+            b.record()
+        torch.cuda.synchronize()
+        return sorted(a.elapsed_time(b) for a, b in evs[1:])
+
+    gemm_ms = bracketed(gemm_only)
+    quant_ms = bracketed(quant_only)
+    del quantised, lora_ts
+
+    # ---- end to end: host buffers through the public MODULE call (the ops-class Linear a ComfyUI model is built
+    # from), copies inside the timed region.  The three phases of consecutive steps overlap as a serving loop would
+    # run them: host->device copy on one stream, the forward on the current stream, device->host copy of the result
+    # on a third (PCIe is full duplex); every step still moves its own input and its own output.
+    modules = [make_module(pkg, s, shape) for s in sets]
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     cur = torch.cuda.current_stream(dev)
     x_dev = [torch.empty_like(s["x"]) for s in sets]
+    y_dev = [torch.empty((M, N), dtype=out_dtype, device=dev) for _ in sets]     # copy-only loop's source
     keep = [None] * N_BUFFER_SETS            # outputs stay referenced until their copy-out has been enqueued again
     fwd_done = [torch.cuda.Event() for _ in range(N_BUFFER_SETS)]
     in_done = [torch.cuda.Event() for _ in range(N_BUFFER_SETS)]
     for ev in fwd_done:
         ev.record(cur)
 
-    def e2e_step(i: int):
+    def e2e_step(i: int, compute: bool = True):
         k = i % N_BUFFER_SETS
         s = sets[k]
         with torch.cuda.stream(s_in):
@@ -320,12 +488,7 @@ def run_gpu_arm(args):
             x_dev[k].copy_(s["x_host"], non_blocking=True)
             in_done[k].record(s_in)
         cur.wait_event(in_done[k])
-        xd = x_dev[k]
-        if s["lora"] is not None:
-            q, xs = F.quantize_rowwise(xd, hadamard=shape.hadamard)
-            y = F.linear_w8a8_lora(q, xs, s["wq"], s["ws"], s["bias"], F.lora_down(xd, s["lora"][0]), s["lora"][1], out_dtype)
-        else:
-            y = F.linear_forward(xd, s["wq"], s["ws"], s["bias"], out_dtype, hadamard=shape.hadamard)
+        y = modules[k](x_dev[k]) if compute else y_dev[k]
         fwd_done[k].record(cur)
         keep[k] = y
         y.record_stream(s_out)
@@ -333,58 +496,161 @@ def run_gpu_arm(args):
             s_out.wait_event(fwd_done[k])
             s["y_host"].copy_(y, non_blocking=True)
 
+    def e2e_loop(n, compute):
+        for i in range(3):
+            e2e_step(i, compute)
+        cur.wait_stream(s_out)
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            e2e_step(i, compute)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
+        b.record()
+        sync_all()
+        return a.elapsed_time(b)
+
     e2e_steps = max(3, min(args.steps, 40))
-    for i in range(3):
-        e2e_step(i)
-    cur.wait_stream(s_out)
-    sync_all()
-    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    cur.wait_stream(s_out)
-    cur.wait_stream(s_in)
-    e_end.record()
-    sync_all()
-    e2e_ms = e_start.elapsed_time(e_end)
+    with torch.no_grad():
+        e2e_ms = e2e_loop(e2e_steps, True)
+    copy_ms = e2e_loop(e2e_steps, False)       # the same copies without any kernel: what the host link allows
+    del x_dev, y_dev, keep
     status = nat.device_status()
 
+    elapsed_ms, e2e_ms, copy_ms, gemm_med, quant_med = max_over_ranks(
+        [elapsed_ms, e2e_ms, copy_ms, median(gemm_ms), median(quant_ms)], dev, dist)
+
+    sub = {}
+    rc = 0
+    if extras:
+        sub["sustained"] = sustained_record(step, shape, gemm_only, sets, F, local_rank, rank, dev, dist, sync_all, args.sustained_s)
+        if rank == 0:
+            sub["comparators"] = comparators_record(shape, sets, 20)
+        sync_all()
+    parity_set = {k: sets[0][k] for k in ("x", "wq", "ws", "bias", "lora")}
+    del sets, modules, workspace
+    torch.cuda.empty_cache()
+    if extras:
+        sub["dit"] = dit_record(pkg, args, rank, world, local_rank, dev, dist, steps=10)
+        torch.cuda.empty_cache()
+        if world > 1:
+            sub["c4"] = column_parallel_record(pkg, rank, world, dev, dist, steps=20)
+            if rank == 0 and not sub["c4"]["ok"]:
+                rc = 1
     if dist is not None:
-        t = torch.tensor([elapsed_ms, e2e_ms, gemm_avg_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms, gemm_avg_ms = (float(v) for v in t.tolist())
+        dist.barrier()
         dist.destroy_process_group()
     if rank != 0:
         return
+    parity = parity_record(pkg, shape, parity_set, dev) if (extras or args.parity) else None
+    if parity is not None and not parity["ok"]:
+        rc = 1
 
     ops_step = 2.0 * M * N * K                       # int8 GEMM ops of one rank's step
     value = world * ops_step * args.steps / (elapsed_ms * 1e-3) / 1e12
     e2e_value = world * ops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
     peaks, peak_kind = measured_peaks()
-    # int8 tensor throughput is twice the bf16 rate of the same tensor cores; the steps run back to
-    # back for a short burst, so the burst figure is the denominator
+    # int8 tensor throughput is twice the bf16 rate of the same tensor cores; the kernel is timed in a short
+    # back-to-back loop of its own, so the burst figure is the denominator
     peak_tops = 2.0 * peaks["bf16_tflops"]
-    achieved = ops_step / (gemm_avg_ms * 1e-3) / 1e12
+    achieved = ops_step / (gemm_med * 1e-3) / 1e12
     cpu_base, _ = cpu_reference_rate(shape, steps=20, warmup=2, budget_s=12.0)
+    k1_bytes = M * K * 3 + 4 * M
     line = {
         "metric": "w8a8_linear_int8_throughput", "value": value, "unit": "TOPS", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": config_dict(shape, world),
         "frac_of_nominal_int8_peak": value / (world * NOMINAL_INT8_TOPS),
-        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8, pair" + (", fused LoRA>" if shape.lora_rank else ">"), "achieved": achieved, "peak": peak_tops,
-                     "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": NCU_GEMM_TRAFFIC_BYTES.get(shape.name),
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8, pair" + (", fused LoRA>" if shape.lora_rank else ">"),
+                     "achieved": achieved, "peak": peak_tops, "unit": "TOPS", "frac": achieved / peak_tops,
+                     "traffic": NCU_GEMM_TRAFFIC_BYTES.get(shape.name),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the capture "
+                                       "summarised in profiles/gemm_tcgen05_i8_pair_c1_quarot_mlp_up.md (not re-measured in this run)",
                      "peak_source": f"2 x bf16_tflops (burst) of {peak_kind} MEASURED_PEAKS.json; int8 ops counted as 2*M*N*K",
-                     "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "kernel_ms_avg": gemm_avg_ms,
-                     "kernel_ms_best": gemm_ms[0], "kernel_launches_timed": len(gemm_ms)},
+                     "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS, "kernel_ms_median": gemm_med,
+                     "kernel_ms_best": gemm_ms[0], "kernel_ms_n": len(gemm_ms),
+                     "timing": f"{len(gemm_ms)} event-bracketed launches of the GEMM alone, back to back over the rotating "
+                               "buffer sets, after the headline loop; first launch discarded; median (max over ranks)",
+                     "quant_kernel": {"kernel": "quant_rows_kernel" + (" (with the Hadamard rotation)" if shape.hadamard else ""),
+                                      "bound": "hbm", "kernel_ms_median": quant_med, "kernel_ms_best": quant_ms[0],
+                                      "kernel_ms_n": len(quant_ms), "algorithmic_bytes": k1_bytes,
+                                      "achieved": k1_bytes / (quant_med * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": k1_bytes / (quant_med * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+                     "kernels_sum_vs_step_ms": [gemm_med + quant_med, elapsed_ms / args.steps]},
         "cpu_baseline": cpu_base,
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
-                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "call": "StandaloneInt8Ops.Linear.forward (the ops-class module) on a device copy of the pinned host input",
+                "copy_only_ms_per_step": copy_ms / e2e_steps, "frac_of_copy_roofline": copy_ms / e2e_ms,
+                "copy_roofline": "the same pinned H2D + D2H copies on the same three streams with no kernel in between "
+                                 "(max over ranks): what the host link delivers to all ranks at once"},
         "gpu_launches": int(launches_timed) * world,
         "clocks": clocks,
         "device_status": status,
     }
+    if parity is not None:
+        line["parity"] = parity
+    line.update(sub)
     print(json.dumps(line))
+    if rc:
+        sys.exit(rc)
+
+
+def sustained_record(step, shape, gemm_only, sets, F, local_rank, rank, dev, dist, sync_all, seconds: float):
+    """The headline step back to back for `seconds` (the chip is power-managed: a 20-step burst runs at the idle
+    clock, steady state does not).  The GEMM alone is event-bracketed on every 64th step, which replaces that step's
+    fused call by the two separate entry points."""
+    import torch
+    M, K, N = shape.M, shape.K, shape.N
+    n_probe = 200
+    sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(n_probe):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    est_ms = a.elapsed_time(b) / n_probe
+    n = int(max(n_probe, min(40000, seconds * 1e3 / est_ms)))
+    sampler = ClockSampler(local_rank, period_s=0.02) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    sync_all()
+    evs = []
+    h0 = time.perf_counter()
+    a.record()
+    for i in range(n):
+        if i % 64 == 63:
+            s = sets[i % N_BUFFER_SETS]
+            q, xs = F.quantize_rowwise(s["x"], hadamard=shape.hadamard)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            F.linear_w8a8(q, xs, s["wq"], s["ws"], s["bias"], torch.bfloat16)
+            e1.record()
+            evs.append((e0, e1))
+        else:
+            step(i)
+    b.record()
+    sync_all()
+    h1 = time.perf_counter()
+    ms = a.elapsed_time(b) / n
+    clocks = sampler.stop(h0, h1) if sampler else None
+    k2 = sorted(x.elapsed_time(y) for x, y in evs) if shape.lora_rank == 0 else [float("nan")]
+    ms, k2_med = max_over_ranks([ms, median(k2)], dev, dist)
+    peaks, kind = measured_peaks()
+    ops = 2.0 * M * N * K
+    rec = {"seconds": ms * n / 1e3, "steps": n, "ms_per_step": ms, "tops_per_gpu": ops / (ms * 1e-3) / 1e12,
+           "gemm_ms_median": k2_med, "gemm_tops": ops / (k2_med * 1e-3) / 1e12, "gemm_samples": len(k2),
+           "frac_of_2x_bf16_sustained": ops / (k2_med * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops_sustained"]),
+           "frac_of_nominal_4500": ops / (k2_med * 1e-3) / 1e12 / NOMINAL_INT8_TOPS,
+           "peak_source": f"2 x bf16_tflops_sustained of {kind} MEASURED_PEAKS.json", "clocks": clocks}
+    if clocks and clocks.get("sm_mhz"):
+        # time x clock = cycles: compares burst and sustained numbers clock for clock
+        rec["gemm_ms_times_sm_mhz"] = k2_med * clocks["sm_mhz"]
+        rec["step_ms_times_sm_mhz"] = ms * clocks["sm_mhz"]
+    return rec
 
 
 # ------------------------------------------------------------- DiT workload
@@ -411,36 +677,14 @@ def dit_cpu_seconds(cfg, budget_s: float):
     return cfg.int8_ops() / (tops * 1e12), rates[0]
 
 
-def run_dit(args):
+def dit_record(pkg, args, rank, world, local_rank, dev, dist, steps: int, graph_wanted: bool = True):
+    """Times the synthetic DiT denoising step on every rank (one sample per GPU, no communication) and returns the
+    measurements (max over ranks) as a dict; rank 0's dict is the one that is printed."""
     import importlib
     import torch
-    import __graft_entry__ as g
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    pkg = g.load_package()
     dit = importlib.import_module(pkg.__name__ + ".dit")
     cfg = dit.DiTConfig()
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        sec, base = dit_cpu_seconds(cfg, budget_s=40.0)
-        base = dict(base, value=sec, unit="s/it", sample=base["sample"] + "; step time = int8 ops / that rate")
-        print(json.dumps({"impl": "reference", "metric": "dit_step_time", "value": sec, "unit": "s/it", "n_gpus": args.gpus,
-                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False,
-                          "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                          "config": dit_config_dict(cfg, max(1, args.gpus), False), "cpu_baseline": base,
-                          "e2e": {"value": sec, "unit": "s/it", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                          "gpu_launches": 0}))
-        return
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+    sync_all = make_sync(dist)
     model = dit.SyntheticDiT(cfg, seed=0, device=dev)
     gen = torch.Generator().manual_seed(1000 + rank)
     img_h = torch.randn(1, cfg.img_tokens, cfg.in_channels, generator=gen).bfloat16().pin_memory()
@@ -448,19 +692,17 @@ def run_dit(args):
     out_h = torch.empty(1, cfg.img_tokens, cfg.in_channels, dtype=torch.bfloat16).pin_memory()
     img, txt = img_h.to(dev), txt_h.to(dev)
     t = torch.full((1,), 0.5, device=dev)
-    steps = min(args.steps, 20)
+    nat = pkg._native
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for _ in range(max(3, min(args.warmup, 5))):
+    for _ in range(3):
         out = model(img, txt, t)
     sync_all()
+    eager_out = out.clone()
+    launches0 = nat.load().i8f_launch_count()
+    model(img, txt, t)
+    launches_per_step = int(nat.load().i8f_launch_count() - launches0)
     graph = None
-    if not args.no_graph:
+    if graph_wanted:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -487,7 +729,8 @@ def run_dit(args):
     for _ in range(3):
         step()
     sync_all()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    replay_equals_eager = bool(torch.equal(out, eager_out)) if graph is not None else None
+    sampler = ClockSampler(local_rank, period_s=0.02) if rank == 0 else None
     if sampler:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -515,56 +758,174 @@ def run_dit(args):
     e1.record()
     sync_all()
     e2e_ms = e0.elapsed_time(e1) / steps
-    status = pkg._native.device_status()
+    status = nat.device_status()
     finite = bool(torch.isfinite(out.float()).all())
-    if dist is not None:
-        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = (float(v) for v in tt.tolist())
-        dist.destroy_process_group()
-    if rank != 0:
-        return
-    n_int8 = cfg.double_blocks * 8 + cfg.single_blocks * 2
+    ms, e2e_ms = max_over_ranks([ms, e2e_ms], dev, dist)
+    del model, graph
     peaks, peak_kind = measured_peaks()
     peak_tops = 2.0 * peaks["bf16_tflops_sustained"]
     achieved = cfg.int8_ops() / (ms * 1e-3) / 1e12
+    return {"ms_per_step": ms, "s_per_it": ms * 1e-3, "steps": steps, "cuda_graph": graph_wanted and replay_equals_eager is not None,
+            "graph_replay_equals_eager": replay_equals_eager, "samples_per_s_all_gpus": world / (ms * 1e-3),
+            "n_gpus": world, "parallelism": f"one 1024x1024 sample per GPU x{world}, no communication",
+            "int8_TOP_per_step": cfg.int8_ops() / 1e12, "attention_TFLOP_per_step": cfg.attention_flops() / 1e12,
+            "int8_params_B": cfg.int8_params() / 1e9, "int8_tops_over_whole_step": achieved,
+            "frac_of_2x_bf16_sustained_whole_step": achieved / peak_tops, "peak_source": f"{peak_kind} MEASURED_PEAKS.json",
+            "e2e_ms_per_step": e2e_ms, "h2d_bytes_per_step": img_h.numel() * 2 + txt_h.numel() * 2,
+            "d2h_bytes_per_step": out_h.numel() * 2, "library_launches_per_step": launches_per_step,
+            "clocks": clocks, "device_status": status, "output_finite": finite}
+
+
+def run_dit(args):
+    import importlib
+    import torch
+    import __graft_entry__ as g
+    pkg = g.load_package()
+    dit = importlib.import_module(pkg.__name__ + ".dit")
+    cfg = dit.DiTConfig()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        sec, base = dit_cpu_seconds(cfg, budget_s=40.0)
+        base = dict(base, value=sec, unit="s/it", sample=base["sample"] + "; step time = int8 ops / that rate")
+        print(json.dumps({"impl": "reference", "metric": "dit_step_time", "value": sec, "unit": "s/it", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                          "config": dit_config_dict(cfg, max(1, args.gpus), False), "cpu_baseline": base,
+                          "e2e": {"value": sec, "unit": "s/it", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+    rank, world, local_rank, dev, dist = rank_context()
+    steps = min(args.steps, 20)
+    rec = dit_record(pkg, args, rank, world, local_rank, dev, dist, steps, graph_wanted=not args.no_graph)
+    if dist is not None:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = rec["ms_per_step"]
+    peaks, peak_kind = measured_peaks()
+    peak_tops = 2.0 * peaks["bf16_tflops_sustained"]
+    achieved = rec["int8_tops_over_whole_step"]
     cpu_sec, cpu_base = dit_cpu_seconds(cfg, budget_s=12.0)
     cpu_base = dict(cpu_base, value=cpu_sec, unit="s/it", sample=cpu_base["sample"] + "; step time = int8 ops / that rate")
     print(json.dumps({
         "metric": "dit_step_time", "value": ms * 1e-3, "unit": "s/it", "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8", "data": "synthetic", "config": dit_config_dict(cfg, world, graph is not None),
-        "samples_per_s_all_gpus": world / (ms * 1e-3),
+        "dtype": "int8", "data": "synthetic", "config": dit_config_dict(cfg, world, rec["cuda_graph"]),
+        "samples_per_s_all_gpus": world / (ms * 1e-3), "graph_replay_equals_eager": rec["graph_replay_equals_eager"],
         "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<i8,256> (whole step)", "achieved": achieved,
-                     "peak": peak_tops, "unit": "TFLOP/s", "frac": achieved / peak_tops, "traffic": None,
+                     "peak": peak_tops, "unit": "TOPS", "frac": achieved / peak_tops, "traffic": None,
                      "peak_source": f"2 x bf16_tflops_sustained of {peak_kind} MEASURED_PEAKS.json; achieved = int8 linear ops "
                                     "/ WHOLE step time (attention, norms and element-wise work included in the time)",
                      "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
         "cpu_baseline": cpu_base,
-        "e2e": {"value": e2e_ms * 1e-3, "unit": "s/it", "h2d_bytes_per_step": img_h.numel() * 2 + txt_h.numel() * 2,
-                "d2h_bytes_per_step": out_h.numel() * 2, "steps": steps},
-        "gpu_launches": 2 * n_int8 * steps * world, "clocks": clocks, "device_status": status, "output_finite": finite}))
+        "e2e": {"value": rec["e2e_ms_per_step"] * 1e-3, "unit": "s/it", "h2d_bytes_per_step": rec["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": rec["d2h_bytes_per_step"], "steps": steps},
+        "gpu_launches": rec["library_launches_per_step"] * steps * world, "clocks": rec["clocks"],
+        "device_status": rec["device_status"], "output_finite": rec["output_finite"]}))
 
 
 # ------------------------------------------- column-parallel sweep (config 4)
 NVLINK_PEER_GBS = 770.0   # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
 
 
+def column_parallel_record(pkg, rank, world, dev, dist, steps: int, m_sweep=(1024, 4096, 16384, 32768)):
+    """W8A8 linear K=4096, N=16384 split over the ranks by output channel; every rank quantises the full x and runs
+    its slice.  The bf16 [M, N/P] blocks are gathered two ways: NCCL all-gather (blocks as they land, and with the
+    row-major re-layout), and the fused form whose GEMM epilogue stores every tile into all ranks' buffers over
+    NVLink.  Also checks, on every rank, that the fused result equals the NCCL one and, at M = 1024, that the
+    gathered [M, N] equals the unsharded computation of the same inputs bit for bit."""
+    import torch
+    F, par, wl = pkg.functional, pkg.parallel, pkg.workloads
+    K, N = 4096, 16384
+    w = wl.weight_fp32(N, K, seed=4)
+    b0, e0_ = par.shard_bounds(N, world, rank)
+    wq_full, ws_full = F.quantize_weight_rows(w.to(dev))            # per-channel scales: row-local, shard = slice
+    shard = par.shard_columns(wq_full, ws_full, None, world, rank)
+    wq, ws = shard.weight, shard.weight_scale
+    n_local = e0_ - b0
+    results = []
+    all_ok = True
+    fused = par.FusedColumnParallelOutput(max(m_sweep), N, torch.bfloat16, dev)
+    for M in m_sweep:
+        x = wl.activation(M, K, seed=40).to(dev)          # same bits on every rank
+        gathered = torch.empty((world * M, n_local), dtype=torch.bfloat16, device=dev)   # [P, M, N/P] blocks
+        full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+
+        def step_nccl(relayout: bool):
+            q, xs = F.quantize_rowwise(x)
+            y = F.linear_w8a8(q, xs, wq, ws, None, torch.bfloat16)
+            dist.all_gather_into_tensor(gathered, y)
+            if relayout:
+                full.view(M, world, n_local).copy_(gathered.view(world, M, n_local).transpose(0, 1))
+            return y
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            dist.barrier()
+            return max_over_ranks([a.elapsed_time(b) / steps], dev, dist)[0]
+
+        ms_blocks = timed(lambda: step_nccl(False))
+        ms_full = timed(lambda: step_nccl(True))
+        ms_fused = timed(lambda: fused.forward(x, shard))
+        y_all = fused.forward(x, shard)
+        step_nccl(True)
+        torch.cuda.synchronize()
+        flags = [1.0 if torch.equal(y_all, full) else 0.0]
+        if M == min(m_sweep):
+            unsharded = F.linear_forward(x, wq_full, ws_full, None, torch.bfloat16)
+            flags.append(1.0 if torch.equal(full, unsharded) and torch.equal(y_all, unsharded) else 0.0)
+            del unsharded
+        if dist is not None:
+            t = torch.tensor(flags, device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)          # true only if true on every rank
+            flags = t.tolist()
+        ops = 2.0 * M * N * K
+        comm_bytes = 2.0 * M * N * (world - 1) / world
+        nvlink_ms = comm_bytes / (NVLINK_PEER_GBS * 1e9) * 1e3
+        rec = {"M": M, "ms_fused_epilogue_scatter": ms_fused, "ms_nccl_blocks_layout": ms_blocks,
+               "ms_nccl_row_major_layout": ms_full, "fused_equals_nccl_result": bool(flags[0] == 1.0),
+               "tops_fused": ops / (ms_fused * 1e-3) / 1e12, "allgather_bytes_in_per_gpu": comm_bytes,
+               "nvlink_roofline_ms": nvlink_ms, "frac_of_nvlink_roofline_fused": nvlink_ms / ms_fused,
+               "frac_of_nvlink_roofline_nccl_blocks": nvlink_ms / ms_blocks}
+        if len(flags) > 1:
+            rec["equals_unsharded"] = bool(flags[1] == 1.0)
+            all_ok = all_ok and rec["equals_unsharded"]
+        all_ok = all_ok and rec["fused_equals_nccl_result"]
+        results.append(rec)
+        del x, gathered, full, y_all
+    torch.cuda.synchronize()
+    status = pkg._native.device_status()
+    status = int(max_over_ranks([status], dev, dist)[0])
+    del fused
+    return {"workload": "c4_column_parallel", "K": K, "N": N, "n_gpus": world, "steps": steps,
+            "parallelism": f"column-parallel x{world}: NCCL all-gather of bf16 [M, N/P] blocks vs GEMM-epilogue scatter over NVLink",
+            "sweep": results, "device_status": status, "ok": bool(all_ok and status == 0),
+            "nvlink_peer_gbs": NVLINK_PEER_GBS,
+            "note": "communication-bound by construction (bytes per op fixed by K): the roofline is NVLink, "
+                    f"{NVLINK_PEER_GBS} GB/s per direction per GPU (measured peer copy); weights (64 MB / P per rank) stay "
+                    "L2-resident across steps"}
+
+
 def run_column_parallel(args):
-    """W8A8 linear K=4096, N=16384 split over the ranks by output channel; every rank quantises the full x, runs
-    its slice and the bf16 [M, N/P] blocks are all-gathered (NCCL).  One line with a result per M."""
+    """One line with a result per M of the column-parallel sweep (needs more than one rank)."""
     import torch
     import __graft_entry__ as g
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     K, N = 4096, 16384
-    m_sweep = [1024, 4096, 16384, 32768]
     if args.impl == "reference":
-        if rank != 0:
+        if int(os.environ.get("RANK", "0")) != 0:
             return
-        import __graft_entry__ as g2
-        wl = g2.load_package().workloads
+        wl = g.load_package().workloads
         base, dt = cpu_reference_rate(wl.LinearShape("c4_column_parallel", 4096, K, N, False, True, False), args.steps,
                                       args.warmup, budget_s=40.0)
         print(json.dumps({"impl": "reference", "metric": "w8a8_linear_int8_throughput", "value": base["value"], "unit": "TOPS",
@@ -574,100 +935,27 @@ def run_column_parallel(args):
                           "cpu_baseline": base, "gpu_launches": 0,
                           "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    import torch.distributed as dist
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    rank, world, local_rank, dev, dist = rank_context()
+    if world < 2:
+        raise SystemExit("the column-parallel sweep needs at least two ranks (torchrun --nproc-per-node N bench.py --workload c4)")
     pkg = g.load_package()
-    F, par, wl = pkg.functional, pkg.parallel, pkg.workloads
-    w = wl.weight_fp32(N, K, seed=4)
-    b0, e0_ = par.shard_bounds(N, world, rank)
-    wq, ws = F.quantize_weight_rows(w[b0:e0_].to(dev))
-    n_local = e0_ - b0
     steps = min(args.steps, 50)
-    results = []
-    for M in m_sweep:
-        x = wl.activation(M, K, seed=40).to(dev)          # same bits on every rank
-        gathered = torch.empty((world * M, n_local), dtype=torch.bfloat16, device=dev)   # [P, M, N/P] blocks
-        full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-
-        def step(relayout: bool):
-            q, xs = F.quantize_rowwise(x)
-            y = F.linear_w8a8(q, xs, wq, ws, None, torch.bfloat16)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered, y)
-                if relayout:
-                    full.view(M, world, n_local).copy_(gathered.view(world, M, n_local).transpose(0, 1))
-            return y
-
-        def timed(relayout: bool):
-            for _ in range(3):
-                step(relayout)
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-                torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for _ in range(steps):
-                step(relayout)
-            b.record()
-            torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
-            t = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-
-        ms_blocks = timed(False)
-        ms_full = timed(True) if world > 1 else ms_blocks
-        ms_fused, fused_equal = None, None
-        if world > 1 and n_local % 32 == 0:
-            try:
-                shard = par.ColumnShard(wq, ws, None, b0, e0_, N)
-                fused = par.FusedColumnParallelOutput(M, N, torch.bfloat16, dev)
-                step_nccl = step
-
-                def step(relayout: bool):       # noqa: F811 - same timing harness, fused kernel
-                    return fused.forward(x, shard)
-
-                ms_fused = timed(False)
-                y_all = fused.forward(x, shard)
-                torch.cuda.synchronize()
-                step = step_nccl
-                step(True)
-                torch.cuda.synchronize()
-                fused_equal = bool(torch.equal(y_all, full))
-                del fused
-            except Exception as e:  # noqa: BLE001
-                ms_fused, fused_equal = None, f"unavailable: {e!r}"
-        # parity of the gathered result with the unsharded computation on rank 0's slice of columns
-        ops = 2.0 * M * N * K
-        comm_bytes = 2.0 * M * N * (world - 1) / world
-        nvlink_ms = comm_bytes / (NVLINK_PEER_GBS * 1e9) * 1e3
-        results.append({"M": M, "ms_fused_epilogue_scatter": ms_fused, "fused_equals_nccl_result": fused_equal,
-                        "frac_of_nvlink_roofline_fused": (nvlink_ms / ms_fused) if ms_fused else None,
-                        "ms_blocks_layout": ms_blocks, "ms_row_major_layout": ms_full,
-                        "tops": ops / (ms_blocks * 1e-3) / 1e12, "allgather_bytes_in_per_gpu": comm_bytes,
-                        "nvlink_roofline_ms": nvlink_ms, "frac_of_nvlink_roofline": (nvlink_ms / ms_blocks) if world > 1 else None})
-        del x, gathered, full
-    status = pkg._native.device_status()
-    if world > 1:
-        dist.destroy_process_group()
+    rec = column_parallel_record(pkg, rank, world, dev, dist, steps)
+    dist.barrier()
+    dist.destroy_process_group()
     if rank != 0:
         return
-    ref = next(r for r in results if r["M"] == 4096)
-    print(json.dumps({"metric": "w8a8_linear_int8_throughput", "value": ref["tops"], "unit": "TOPS", "n_gpus": world,
-                      "steps": steps, "warmup": 3, "ms_per_step": ref["ms_blocks_layout"], "higher_is_better": True,
+    ref = next(r for r in rec["sweep"] if r["M"] == 4096)
+    print(json.dumps({"metric": "w8a8_linear_int8_throughput", "value": ref["tops_fused"], "unit": "TOPS", "n_gpus": world,
+                      "steps": steps, "warmup": 3, "ms_per_step": ref["ms_fused_epilogue_scatter"], "higher_is_better": True,
                       "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                       "config": {"workload": "c4_column_parallel", "K": K, "N": N, "M": 4096, "weight_scale": "per_channel",
-                                 "parallelism": f"column-parallel x{world}, NCCL all-gather of bf16 [M, N/P] blocks",
+                                 "parallelism": rec["parallelism"],
                                  "l2": "weights 64 MB / P per rank stay L2-resident across steps (real layers would not)"},
-                      "sweep": results, "gpu_launches": 2 * steps * world * len(m_sweep) * 2, "device_status": status,
-                      "note": "communication-bound by construction: bytes/op ratio is fixed by K; roofline is NVLink, "
-                              f"{NVLINK_PEER_GBS} GB/s per direction per GPU (measured peer copy)"}))
+                      "sweep": rec["sweep"], "gpu_launches": 4 * steps * world, "device_status": rec["device_status"],
+                      "ok": rec["ok"], "note": rec["note"]}))
+    if not rec["ok"]:
+        sys.exit(1)
 
 
 # ------------------------------------------- stochastic LoRA merge (config 2, second variant)
@@ -920,6 +1208,10 @@ def main():
     ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="c1: skip the sub-records (sustained loop, comparators, DiT step, column-parallel sweep, parity)")
+    ap.add_argument("--parity", action="store_true", help="with --headline-only or another workload: still log the parity record")
+    ap.add_argument("--sustained-s", type=float, default=2.5, help="length of the sustained-load loop in seconds")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
