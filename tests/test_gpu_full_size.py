@@ -6,7 +6,8 @@ the synthetic DiT and of the column-parallel sweep).  The oracle side runs on th
 and the quantisers from `oracle/bitspec.py` (NumPy), the exact int8 product through `torch._int_mm` on CPU
 tensors and the reference's epilogue expressions from `oracle/torch_path.py` (int8_quant.py:77-88, :107-119).
 Bars: int8 tensors, scales and int32 accumulators equal; 16-bit outputs equal for the plain linear (its
-epilogue is deterministic fp32) and within max|d| <= 1e-2 * RMS where a tensor-core fp32 sum is involved.
+epilogue is deterministic fp32); where a tensor-core fp32 sum is involved (the dynamic-LoRA term) every output
+within one bf16 step of the oracle and within max|d| <= 1e-2 * RMS wherever a bf16 step is smaller than that.
 """
 import numpy as np
 import pytest
@@ -82,11 +83,20 @@ def test_c2_dynamic_lora_full_size(cuda_pkg):
     assert torch.equal(_bits(plain), _bits(base)), "dequant + bias before the LoRA term"
     t = F.lora_down(xd, lora_a.to(DEV))
     y = F.linear_w8a8_lora(q, xs, wqd, wsd, bd, t, lora_b.to(DEV), torch.bfloat16).cpu()
-    err = (y.float() - want.float()).abs().max().item()
-    assert err <= TOL * _rms(want.float()), f"fused LoRA output off by {err}"
-    # the low-rank products run on tensor cores (fp32 partial sums in another order than the CPU library's), so a
-    # few outputs land one bf16 step away; anything more would be an error in the fused path
+    # The low-rank products run on tensor cores (fp32 partial sums in another order than the CPU library's), so a few
+    # outputs land on the neighbouring bf16 value.  At this size the outputs reach |y| ~ 16 with RMS 3.2: one bf16
+    # step at 8..16 is 0.0625 = 2e-2 RMS, so a single step at the top of the range is already above 1e-2 RMS, which
+    # the reference's own CPU and GPU runs would also show against each other.  The bar here: every element within
+    # ONE bf16 step of the oracle, at most 2 % of them off at all, and the error of the whole tensor far below
+    # 1e-2 RMS in the root-mean-square sense.
+    d = (y.float() - want.float()).abs()
+    step = torch.maximum(want.float().abs(), y.float().abs()).clamp_min(2.0 ** -126)
+    step = torch.exp2(torch.floor(torch.log2(step)) - 7)             # bf16 spacing at that magnitude
+    assert bool((d <= step).all()), f"an output is more than one bf16 step off (max {d.max().item()})"
     assert (_bits(y) != _bits(want)).float().mean().item() <= 0.02
+    assert float(d.double().pow(2).mean().sqrt()) <= 1e-3 * _rms(want.float())
+    small = want.float().abs() < 4.0                                  # where a bf16 step is below 1e-2 RMS
+    assert d[small].max().item() <= TOL * _rms(want.float())
     assert cuda_pkg._native.device_status() == 0
 
 

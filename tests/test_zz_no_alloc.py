@@ -15,6 +15,9 @@ import ctypes
 import pytest
 import torch
 
+from oracle import bitspec as bs
+from oracle import torch_path as tp
+
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
@@ -37,17 +40,34 @@ def test_static_workspace_forward_matches_twice_in_a_row(cuda_pkg):
     F, nat = cuda_pkg.functional, cuda_pkg._native
     cases = [(1024, 2048, 1536, 21, True, False, True),     # first call fills a large part of the array
              (200, 512, 328, 22, False, True, False)]       # second, smaller call runs over the leftovers
+    warmed = False
     for M, K, N, seed, per_channel, hadamard, with_bias in cases:
         x, wq, ws, bias = _case(cuda_pkg, M, K, N, seed, per_channel, hadamard, with_bias)
         want = F.linear_forward(x, wq, ws, bias, torch.bfloat16, hadamard=hadamard)
         out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)   # the caller owns the output
+        if not warmed:
+            # The FIRST call on a device is where the driver gives the built-in array its memory (lazy module
+            # loading), so device memory in use may grow by the array's size here -- once.
+            F.linear_forward_static(x, wq, ws, bias, out, hadamard=hadamard)
+            warmed = True
         torch.cuda.synchronize()
         before = torch.cuda.memory_stats(DEV)["allocation.all.allocated"]      # running count of allocator requests
+        free_before, _ = torch.cuda.mem_get_info(DEV)                           # what the DRIVER has left
         got = F.linear_forward_static(x, wq, ws, bias, out, hadamard=hadamard)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(DEV)
         after = torch.cuda.memory_stats(DEV)["allocation.all.allocated"]
         assert after == before, f"the wrapper must not allocate through torch either ({after - before} new blocks)"
+        # torch's counter cannot see allocations made behind its back; the driver's free-memory figure can
+        assert free_after >= free_before, f"device memory in use grew by {free_before - free_after} bytes during the call"
         assert got is out
+        # and against the CPU oracle directly, not only against the sibling entry point
+        x_cpu = x.cpu()
+        if hadamard:
+            x_cpu = torch.from_numpy(bs.rotate_activation(x_cpu.float().numpy(), "bf16")).bfloat16()
+        oracle = tp.linear_w8a8(x_cpu, wq.cpu(), ws.cpu().reshape(-1, 1) if per_channel else float(ws.cpu()[0]),
+                                None if bias is None else bias.cpu(), torch.bfloat16)
+        assert torch.equal(got.cpu().view(torch.int16), oracle.view(torch.int16))
         # tolerance used by the linear tests: 1e-2 * RMS in max-abs; the two entry points share every
         # kernel, so they are in fact bit-identical
         rms = want.float().pow(2).mean().sqrt().item()
