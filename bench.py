@@ -708,7 +708,7 @@ def dit_cpu_seconds(cfg, budget_s: float):
     return cfg.int8_ops() / (tops * 1e12), rates[0]
 
 
-def dit_record(pkg, args, rank, world, local_rank, dev, dist, steps: int, graph_wanted: bool = True):
+def dit_record(pkg, args, rank, world, local_rank, dev, dist, steps: int, graph_wanted: bool = True, fused: bool = True):
     """Times the synthetic DiT denoising step on every rank (one sample per GPU, no communication) and returns the
     measurements (max over ranks) as a dict; rank 0's dict is the one that is printed."""
     import importlib
@@ -716,7 +716,7 @@ def dit_record(pkg, args, rank, world, local_rank, dev, dist, steps: int, graph_
     dit = importlib.import_module(pkg.__name__ + ".dit")
     cfg = dit.DiTConfig()
     sync_all = make_sync(dist)
-    model = dit.SyntheticDiT(cfg, seed=0, device=dev)
+    model = dit.SyntheticDiT(cfg, seed=0, device=dev, fused=fused)
     gen = torch.Generator().manual_seed(1000 + rank)
     img_h = torch.randn(1, cfg.img_tokens, cfg.in_channels, generator=gen).bfloat16().pin_memory()
     txt_h = torch.randn(1, cfg.txt_tokens, cfg.txt_dim, generator=gen).bfloat16().pin_memory()
@@ -796,7 +796,9 @@ def dit_record(pkg, args, rank, world, local_rank, dev, dist, steps: int, graph_
     peaks, peak_kind = measured_peaks()
     peak_tops = 2.0 * peaks["bf16_tflops_sustained"]
     achieved = cfg.int8_ops() / (ms * 1e-3) / 1e12
-    return {"ms_per_step": ms, "s_per_it": ms * 1e-3, "steps": steps, "cuda_graph": graph_wanted and replay_equals_eager is not None,
+    return {"ms_per_step": ms, "s_per_it": ms * 1e-3, "steps": steps,
+            "block_code": "fused (LayerNorm+modulate and GELU inside the quantiser, one qkv buffer, per-head RMS-norm kernel)"
+                          if fused else "unfused (every element-wise step its own PyTorch call)", "cuda_graph": graph_wanted and replay_equals_eager is not None,
             "graph_replay_equals_eager": replay_equals_eager, "samples_per_s_all_gpus": world / (ms * 1e-3),
             "n_gpus": world, "parallelism": f"one 1024x1024 sample per GPU x{world}, no communication",
             "int8_TOP_per_step": cfg.int8_ops() / 1e12, "attention_TFLOP_per_step": cfg.attention_flops() / 1e12,
@@ -828,7 +830,8 @@ def run_dit(args):
         return
     rank, world, local_rank, dev, dist = rank_context()
     steps = min(args.steps, 20)
-    rec = dit_record(pkg, args, rank, world, local_rank, dev, dist, steps, graph_wanted=not args.no_graph)
+    rec = dit_record(pkg, args, rank, world, local_rank, dev, dist, steps, graph_wanted=not args.no_graph,
+                     fused=not args.dit_unfused)
     if dist is not None:
         dist.destroy_process_group()
     if rank != 0:
@@ -1238,6 +1241,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--dit-unfused", action="store_true",
+                    help="dit: the block code without the fused quantiser prologues (every element-wise step a PyTorch call)")
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--headline-only", action="store_true",
                     help="c1: skip the sub-records (sustained loop, comparators, DiT step, column-parallel sweep, parity)")

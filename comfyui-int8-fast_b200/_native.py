@@ -35,6 +35,11 @@ _PROTOTYPES = {
     "i8f_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "i8f_quant_rowwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                   c_void_p, c_void_p]),
+    "i8f_quant_rowwise_ln_modulate": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_float, c_void_p,
+                                              c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+    "i8f_quant_rowwise_gelu": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int64, c_void_p, c_int64,
+                                       c_void_p, c_void_p, c_int64, c_void_p]),
+    "i8f_rmsnorm_heads": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_float, c_void_p]),
     "i8f_quant_tensorwise": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                                      c_void_p, c_void_p]),
     "i8f_quant_weight_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,

@@ -20,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB = HERE / "libi8f.so"
 OBJ_DIR = HERE / "build"
 SOURCES = ["api.cu", "quant_rowwise.cu", "gemm_tcgen05.cu", "lora_merge_sr.cu", "linear_static.cu",
-           "linear_small_m.cu", "peer_barrier.cu"]
+           "linear_small_m.cu", "peer_barrier.cu", "quant_prologue.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

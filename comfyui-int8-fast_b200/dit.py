@@ -17,6 +17,7 @@ import torch
 import torch.nn.functional as TF
 from torch import Tensor, nn
 
+from . import functional as F
 from .ops import StandaloneInt8Ops as Ops
 
 
@@ -78,6 +79,20 @@ def bf16_linear(in_f: int, out_f: int, gen: torch.Generator, device) -> nn.Linea
     return lin
 
 
+def int8_gemm(lin, q: Tensor, q_scale: Tensor, out: Tensor | None = None) -> Tensor:
+    """The GEMM half of an Int8 Linear on activations that a fused quantiser has already turned into int8."""
+    return F.linear_w8a8(q, q_scale, lin.weight, lin._scale_on(q.device), lin.bias, torch.bfloat16, out=out)
+
+
+def attention_prenormed(qkv: Tensor, heads: int) -> Tensor:
+    """qkv [T, 3*h] whose q and k columns are already RMS-normalised per head -> attention output [T, h]."""
+    t, h3 = qkv.shape
+    h = h3 // 3
+    q, k, v = qkv.view(1, t, 3, heads, h // heads).unbind(2)
+    out = TF.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+    return out.transpose(1, 2).reshape(t, h)
+
+
 def rms_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
     return TF.rms_norm(x, x.shape[-1:], eps=eps)
 
@@ -122,6 +137,31 @@ class DoubleBlock(nn.Module):
         self.img = StreamBlock(cfg, gen, device)
         self.txt = StreamBlock(cfg, gen, device)
 
+    def forward_fused(self, img: Tensor, txt: Tensor, vec: Tensor):
+        """The same block with the element-wise steps around the quantised linears folded into the library's kernels:
+        LayerNorm + modulation and GELU run inside the activation quantiser, both streams' qkv projections write into
+        one buffer, and the per-head RMS norm of q and k is one in-place launch over it.  img [Ti, h], txt [Tt, h]."""
+        cfg = self.cfg
+        h = cfg.hidden
+        n_txt = txt.shape[0]
+        qkv = torch.empty((n_txt + img.shape[0], 3 * h), dtype=torch.bfloat16, device=img.device)
+        mods = {}
+        for name, x, blk, rows in (("txt", txt, self.txt, qkv[:n_txt]), ("img", img, self.img, qkv[n_txt:])):
+            mods[name] = [m.reshape(-1) for m in blk.mod(TF.silu(vec)).chunk(6, dim=-1)]
+            q8, xs = F.quantize_rowwise_ln_modulate(x, mods[name][0], mods[name][1])
+            int8_gemm(blk.qkv, q8, xs, out=rows)
+        F.rmsnorm_heads_(qkv[:, : 2 * h])
+        attn = attention_prenormed(qkv, cfg.heads)
+        outs = []
+        for name, x, blk, a in (("txt", txt, self.txt, attn[:n_txt]), ("img", img, self.img, attn[n_txt:])):
+            sh1, sc1, g1, sh2, sc2, g2 = mods[name]
+            x = torch.addcmul(x, g1, blk.proj(a))
+            q8, xs = F.quantize_rowwise_ln_modulate(x, sh2, sc2)
+            q8, xs = F.quantize_rowwise_gelu(int8_gemm(blk.mlp_up, q8, xs))
+            x = torch.addcmul(x, g2, int8_gemm(blk.mlp_down, q8, xs))
+            outs.append(x)
+        return outs[1], outs[0]
+
     def forward(self, img: Tensor, txt: Tensor, vec: Tensor):
         cfg = self.cfg
         mods = {}
@@ -148,6 +188,18 @@ class SingleBlock(nn.Module):
         self.linear1 = int8_linear(h, 3 * h + m, gen, device)
         self.linear2 = int8_linear(h + m, h, gen, device)
 
+    def forward_fused(self, x: Tensor, vec: Tensor) -> Tensor:
+        """x [T, h].  linear1's input is quantised with LayerNorm + modulation folded in; linear2's input row
+        [ attention | GELU(mlp) ] is assembled and quantised in one pass, never stored in 16 bits."""
+        h = self.cfg.hidden
+        shift, scale, gate = [m.reshape(-1) for m in self.mod(TF.silu(vec)).chunk(3, dim=-1)]
+        q8, xs = F.quantize_rowwise_ln_modulate(x, shift, scale)
+        y = int8_gemm(self.linear1, q8, xs)
+        F.rmsnorm_heads_(y[:, : 2 * h])
+        attn = attention_prenormed(y[:, : 3 * h], self.cfg.heads)
+        q8, xs = F.quantize_rowwise_gelu(y[:, 3 * h:], attn)
+        return torch.addcmul(x, gate, int8_gemm(self.linear2, q8, xs))
+
     def forward(self, x: Tensor, vec: Tensor) -> Tensor:
         h = self.cfg.hidden
         shift, scale, gate = self.mod(TF.silu(vec)).chunk(3, dim=-1)
@@ -167,9 +219,13 @@ def timestep_embedding(t: Tensor, dim: int = 256) -> Tensor:
 
 
 class SyntheticDiT(nn.Module):
-    def __init__(self, cfg: DiTConfig = DiTConfig(), seed: int = 0, device="cuda"):
+    def __init__(self, cfg: DiTConfig = DiTConfig(), seed: int = 0, device="cuda", fused: bool = True):
+        """`fused` selects the block code that uses the library's fused quantiser prologues and the per-head RMS-norm
+        kernel (batch 1, head size 128); otherwise every element-wise step is its own PyTorch call, which is how a
+        model written against the node pack's Linear alone would run."""
         super().__init__()
         self.cfg = cfg
+        self.fused = fused
         gen = torch.Generator(device=device)
         gen.manual_seed(seed)
         h = cfg.hidden
@@ -186,11 +242,20 @@ class SyntheticDiT(nn.Module):
         """img [B, img_tokens, in_channels], txt [B, txt_tokens, txt_dim], t [B] in [0,1] -> velocity [B, img_tokens, in_channels]."""
         vec = self.time_in(timestep_embedding(t).to(torch.bfloat16))
         img, txt = self.img_in(img), self.txt_in(txt)
-        for blk in self.double_stream:
-            img, txt = blk(img, txt, vec)
-        x = torch.cat([txt, img], dim=1)
-        for blk in self.single_stream:
-            x = blk(x, vec)
+        if self.fused and img.shape[0] == 1 and self.cfg.head_dim == 128 and self.cfg.hidden % 8 == 0:
+            img2, txt2 = img[0], txt[0]
+            for blk in self.double_stream:
+                img2, txt2 = blk.forward_fused(img2, txt2, vec)
+            x2 = torch.cat([txt2, img2], dim=0)
+            for blk in self.single_stream:
+                x2 = blk.forward_fused(x2, vec)
+            x = x2[None]
+        else:
+            for blk in self.double_stream:
+                img, txt = blk(img, txt, vec)
+            x = torch.cat([txt, img], dim=1)
+            for blk in self.single_stream:
+                x = blk(x, vec)
         x = x[:, txt.shape[1]:]
         shift, scale = self.final_mod(TF.silu(vec)).chunk(2, dim=-1)
         return self.final(modulate(x, shift, scale))

@@ -80,6 +80,61 @@ def quantize_rowwise(x: Tensor, hadamard: bool = False, return_rotated: bool = F
     return q, scale
 
 
+def quantize_rowwise_ln_modulate(x: Tensor, shift: Tensor, scale: Tensor, eps: float = 1e-5, return_y: bool = False):
+    """Per-token int8 of LayerNorm(x) * (1 + scale) + shift in one pass over x [M,K] (bf16 / fp16; shift, scale [K]).
+
+    Returns (q, row_scale) and, if asked, the modulated activations y in x's dtype (the tensor the unfused model
+    code would have handed to the linear)."""
+    nat.require_device(x.device)
+    x = _rows(x)
+    M, K = x.shape
+    shift = shift.reshape(-1).to(device=x.device, dtype=x.dtype).contiguous()
+    scale = scale.reshape(-1).to(device=x.device, dtype=x.dtype).contiguous()
+    if shift.numel() != K or scale.numel() != K:
+        raise ValueError(f"shift and scale must have {K} elements")
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    rs = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    y = torch.empty((M, K), dtype=x.dtype, device=x.device) if return_y else None
+    if M > 0:
+        nat.check(nat.load().i8f_quant_rowwise_ln_modulate(nat.ptr(x), _code(x.dtype), M, K, _ld(x), nat.ptr(shift), nat.ptr(scale),
+                                                           float(eps), nat.ptr(q), K, nat.ptr(rs), nat.ptr(y), K,
+                                                           nat.current_stream(x.device)), "i8f_quant_rowwise_ln_modulate")
+    return (q, rs, y) if return_y else (q, rs)
+
+
+def quantize_rowwise_gelu(x_gelu: Tensor, x_plain: Tensor | None = None, return_y: bool = False):
+    """Per-token int8 of the row [ x_plain | GELU_tanh(x_gelu) ] in one pass (x_plain may be None).  The two parts may
+    be column slices of wider matrices (unit inner stride, 16-byte aligned)."""
+    nat.require_device(x_gelu.device)
+    if x_gelu.dim() != 2 or x_gelu.stride(1) != 1 or (x_plain is not None and (x_plain.dim() != 2 or x_plain.stride(1) != 1)):
+        raise ValueError("inputs must be 2-D with unit inner stride")
+    M, K1 = x_gelu.shape
+    K0 = 0 if x_plain is None else x_plain.shape[1]
+    if x_plain is not None and (x_plain.shape[0] != M or x_plain.dtype != x_gelu.dtype):
+        raise ValueError("the two parts must have the same rows and dtype")
+    q = torch.empty((M, K0 + K1), dtype=torch.int8, device=x_gelu.device)
+    rs = torch.empty((M, 1), dtype=torch.float32, device=x_gelu.device)
+    y = torch.empty((M, K0 + K1), dtype=x_gelu.dtype, device=x_gelu.device) if return_y else None
+    if M > 0:
+        nat.check(nat.load().i8f_quant_rowwise_gelu(nat.ptr(x_plain), K0, x_plain.stride(0) if x_plain is not None else 0,
+                                                    nat.ptr(x_gelu), K1, x_gelu.stride(0), _code(x_gelu.dtype), M, nat.ptr(q),
+                                                    K0 + K1, nat.ptr(rs), nat.ptr(y), K0 + K1,
+                                                    nat.current_stream(x_gelu.device)), "i8f_quant_rowwise_gelu")
+    return (q, rs, y) if return_y else (q, rs)
+
+
+def rmsnorm_heads_(x: Tensor, eps: float = 1e-6) -> Tensor:
+    """In place RMS norm of every 128-column block of every row of x [rows, cols] (per attention head)."""
+    nat.require_device(x.device)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be 2-D with unit inner stride")
+    rows, cols = x.shape
+    if rows and cols:
+        nat.check(nat.load().i8f_rmsnorm_heads(nat.ptr(x), _code(x.dtype), rows, cols, x.stride(0), float(eps),
+                                               nat.current_stream(x.device)), "i8f_rmsnorm_heads")
+    return x
+
+
 def quantize_weight_rows(w: Tensor, hadamard: bool = False):
     """Per-output-channel weight quantisation in fp32 (rotation, if any, also in fp32)."""
     nat.require_device(w.device)
@@ -123,11 +178,12 @@ def gemm_i8_i32(a: Tensor, w: Tensor) -> Tensor:
 
 
 def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype,
-                order: int = nat.EPI_PYTORCH, add_into: Tensor | None = None) -> Tensor:
+                order: int = nat.EPI_PYTORCH, add_into: Tensor | None = None, out: Tensor | None = None) -> Tensor:
     """Dequantising int8 GEMM from pre-quantised activations.
 
     With `add_into` ([M,N], out_dtype, unit inner stride) the result is added onto what that tensor holds
-    (out = round(round(result) + add_into)), in place, and `add_into` is returned.
+    (out = round(round(result) + add_into)), in place, and `add_into` is returned.  With `out` ([M,N], out_dtype,
+    unit inner stride, e.g. a row or column slice of a wider buffer) the result is written there.
     """
     nat.require_device(q.device)
     q, w = _rows(q), _rows(w)
@@ -142,7 +198,11 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
             raise ValueError("add_into must be [M,N] in out_dtype with unit inner stride")
         out, fn, what = add_into, nat.load().i8f_linear_w8a8_add, "i8f_linear_w8a8_add"
     else:
-        out, fn, what = torch.empty((M, N), dtype=out_dtype, device=q.device), nat.load().i8f_linear_w8a8, "i8f_linear_w8a8"
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=q.device)
+        elif out.shape != (M, N) or out.dtype != out_dtype or out.stride(1) != 1:
+            raise ValueError("out must be [M,N] in out_dtype with unit inner stride")
+        fn, what = nat.load().i8f_linear_w8a8, "i8f_linear_w8a8"
     if M and N:
         nat.check(fn(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w), nat.ptr(ws), mode, nat.ptr(bias),
                      _code(bias.dtype) if bias is not None else 0, nat.ptr(out), _code(out_dtype), _ld(out), M, N, K, order,

@@ -93,6 +93,31 @@ int i8f_quant_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int64_t 
                       int8_t* q, int64_t ldq, float* scale, int hadamard128,
                       void* x_rot_out, void* stream);
 
+/* The activation quantiser with the element-wise step in front of a quantised linear folded in.  The three entry
+ * points below have no counterpart in the reference, which leaves these steps to the model's own PyTorch code
+ * (a diffusion transformer runs LayerNorm -> modulate -> Linear, GELU -> Linear and a per-head RMS norm of q and k
+ * around every quantised linear, each a full pass over the activations that the quantiser then reads again).
+ * Their arithmetic is specified completely, every rounding and the order of every sum, in
+ * comfyui-int8-fast_b200/csrc/quant_prologue.cu; rows are at most 16384 elements, dtype I8F_BF16 or I8F_F16.
+ *
+ * y = rnd(rnd((x - mean) * rstd) * rnd(1 + scale[k]) + shift[k]) over each row of x [M,K] (LayerNorm without
+ * affine parameters, eps added to the variance; shift, scale: [K] in x_dtype), then q, row_scale as
+ * i8f_quant_rowwise computes them from y.  y_out (may be NULL) receives y in x_dtype with pitch ldy. */
+int i8f_quant_rowwise_ln_modulate(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                                  const void* shift, const void* scale, float eps,
+                                  int8_t* q, int64_t ldq, float* row_scale, void* y_out, int64_t ldy, void* stream);
+
+/* y = [ x_plain [M,K0] | rnd(GELU_tanh(x_gelu [M,K1])) ] row by row (either part may be empty), then q [M,K0+K1],
+ * row_scale as i8f_quant_rowwise computes them from y.  The GELU is x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715
+ * x^3), evaluated in correctly rounded fp32 operations only.  y_out (may be NULL) receives y. */
+int i8f_quant_rowwise_gelu(const void* x_plain, int64_t K0, int64_t ld0, const void* x_gelu, int64_t K1, int64_t ld1,
+                           int x_dtype, int64_t M, int8_t* q, int64_t ldq, float* row_scale,
+                           void* y_out, int64_t ldy, void* stream);
+
+/* In place, every 128-column block of every row of x [rows, cols] (one attention head of one token):
+ * x <- rnd(x / sqrt(mean(x^2) + eps)).  cols a multiple of 128.  Pass the q and k columns of a fused qkv buffer. */
+int i8f_rmsnorm_heads(void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ldx, float eps, void* stream);
+
 /* Quantisation with one scale for the whole tensor (weights).
  *   scale_out[0] = max(absmax(x)/127, 1e-30); q as above.
  * `scratch` is 4 bytes of device memory owned by the caller (absmax exchange).

@@ -334,3 +334,107 @@ def philox_uniforms(seed: int, n_rows: int, n_cols: int) -> np.ndarray:
     key[..., 1] = np.uint32((seed >> 32) & 0xFFFFFFFF)
     words = philox4x32_10(ctr, key).reshape(n_rows, groups * 4)[:, :n_cols]
     return (words >> np.uint32(8)).astype(F32) * F32(2.0 ** -24)
+
+
+# --------------------------------------------------------------------------
+# Quantiser prologues (no counterpart in the reference: the model's own element-wise steps in front of a
+# quantised linear, folded into the activation quantiser; defined by comfyui-int8-fast_b200/csrc/quant_prologue.cu)
+# --------------------------------------------------------------------------
+_ROW_THREADS = 128
+
+
+def rowsum128(v: np.ndarray) -> np.ndarray:
+    """Sum of every row of v [M, K] (K % 8 == 0) in the quantiser's fixed order.
+
+    A row belongs to 128 threads; thread t holds the 8-element vectors t, t + 128, ...  Order of the fp32 additions:
+    the 8 elements of a vector left to right; a thread's vector sums in slot order; the 32 lanes of a warp as a
+    balanced binary tree (neighbours first); the four warps left to right.  Vectors past the end count as zeros.
+    """
+    v = np.asarray(v, dtype=F32)
+    M, K = v.shape
+    nvec = K // 8
+    vpt = max(1, -(-nvec // _ROW_THREADS))
+    pad = np.zeros((M, vpt * _ROW_THREADS * 8), dtype=F32)
+    pad[:, :K] = v
+    e = pad.reshape(M, vpt, _ROW_THREADS, 8)
+    s = e[..., 0] + e[..., 1]
+    for j in range(2, 8):
+        s = s + e[..., j]
+    t = s[:, 0, :]
+    for i in range(1, vpt):
+        t = t + s[:, i, :]
+    w = t.reshape(M, 4, 32)
+    while w.shape[-1] > 1:
+        w = w[..., 0::2] + w[..., 1::2]
+    w = w[..., 0]
+    return ((w[:, 0] + w[:, 1]) + w[:, 2]) + w[:, 3]
+
+
+def layernorm_modulate(x: np.ndarray, shift: np.ndarray, scale: np.ndarray, eps: float = 1e-5, dtype: str = "bf16") -> np.ndarray:
+    """y = rnd(rnd((x - mean) * rstd) * rnd(1 + scale) + shift): LayerNorm without affine parameters followed by the
+    adaptive modulation of a diffusion transformer block, every intermediate tensor in the activation dtype."""
+    x = np.asarray(x, dtype=F32)
+    K = F32(x.shape[1])
+    mean = (rowsum128(x) / K).astype(F32)[:, None]
+    d = (x - mean).astype(F32)
+    var = (rowsum128(d * d) / K).astype(F32)[:, None]
+    rstd = (F32(1.0) / np.sqrt((var + F32(eps)).astype(F32))).astype(F32)
+    ln = round_to(d * rstd, dtype)
+    one_plus = round_to(F32(1.0) + np.asarray(scale, dtype=F32).reshape(1, -1), dtype)
+    # ln * one_plus is exact in fp32 (two significands of at most 11 bits), so this is the single rounding of an FMA
+    prod = (ln.astype(np.float64) * one_plus.astype(np.float64))
+    return round_to((prod + np.asarray(shift, dtype=F32).reshape(1, -1).astype(np.float64)).astype(F32), dtype)
+
+
+_GELU_C0 = F32(0.7978845608028654)
+_GELU_C1 = F32(0.035677408136300125)
+_NEG2_LOG2E = F32(-2.8853900817779268)
+_EXP2_A = [F32(0.0013333558146428443), F32(0.009618129107628477), F32(0.05550410866482158), F32(0.2402265069591007),
+           F32(0.6931471805599453)]
+
+
+def gelu_tanh(x: np.ndarray) -> np.ndarray:
+    """x * sigmoid(2u), u = x * (c0 + c1 x^2): the tanh form of GELU with the exponential written out in correctly
+    rounded fp32 multiplications and additions (fp32 result, not yet rounded to the activation dtype)."""
+    x = np.asarray(x, dtype=F32)
+    with np.errstate(over="ignore", under="ignore"):
+        u = x * ((x * x) * _GELU_C1 + _GELU_C0)
+        t = np.clip(u * _NEG2_LOG2E, F32(-125.0), F32(125.0)).astype(F32)
+        n = np.rint(t).astype(F32)
+        f = (t - n).astype(F32)
+        p = _EXP2_A[0] * f + _EXP2_A[1]
+        for a in _EXP2_A[2:]:
+            p = p * f + a
+        p = (p * f + F32(1.0)).astype(F32)
+        e = np.ldexp(p, n.astype(np.int32)).astype(F32)      # exponent arithmetic: exact, stays normal for |n| <= 125
+        return (x * (F32(1.0) / (F32(1.0) + e))).astype(F32)
+
+
+def quantize_rowwise_ln_modulate(x, shift, scale, eps: float = 1e-5, dtype: str = "bf16"):
+    y = layernorm_modulate(x, shift, scale, eps, dtype)
+    q, s = quantize_rowwise(y)
+    return q, s, y
+
+
+def quantize_rowwise_gelu(x_gelu, x_plain=None, dtype: str = "bf16"):
+    y = round_to(gelu_tanh(x_gelu), dtype)
+    if x_plain is not None:
+        y = np.concatenate([np.asarray(x_plain, dtype=F32), y], axis=1)
+    q, s = quantize_rowwise(y)
+    return q, s, y
+
+
+def rmsnorm_heads(x: np.ndarray, eps: float = 1e-6, dtype: str = "bf16") -> np.ndarray:
+    """Per-head RMS norm: every 128-column block of every row, y = rnd(x * (1 / sqrt(sum(x^2) / 128 + eps))).
+    Sum order: 16 lanes of 8 elements, squares summed left to right per lane, lanes as a balanced binary tree."""
+    x = np.asarray(x, dtype=F32)
+    rows, cols = x.shape
+    e = (x * x).astype(F32).reshape(rows, cols // 128, 16, 8)
+    s = e[..., 0] + e[..., 1]
+    for j in range(2, 8):
+        s = s + e[..., j]
+    while s.shape[-1] > 1:
+        s = s[..., 0::2] + s[..., 1::2]
+    ms = (s * F32(0.0078125) + F32(eps)).astype(F32)
+    rstd = (F32(1.0) / np.sqrt(ms)).astype(F32)
+    return round_to(x.reshape(rows, cols // 128, 128) * rstd, dtype).reshape(rows, cols)

@@ -86,13 +86,16 @@ def test_c2_dynamic_lora_full_size(cuda_pkg):
     # The low-rank products run on tensor cores (fp32 partial sums in another order than the CPU library's), so a few
     # outputs land on the neighbouring bf16 value.  At this size the outputs reach |y| ~ 16 with RMS 3.2: one bf16
     # step at 8..16 is 0.0625 = 2e-2 RMS, so a single step at the top of the range is already above 1e-2 RMS, which
-    # the reference's own CPU and GPU runs would also show against each other.  The bar here: every element within
-    # ONE bf16 step of the oracle, at most 2 % of them off at all, and the error of the whole tensor far below
-    # 1e-2 RMS in the root-mean-square sense.
+    # the reference's own CPU and GPU runs would also show against each other.  The LoRA term is itself rounded to
+    # bf16 before it is added (int8_quant.py:769-774), so a one-step difference in it can move the sum by two steps.
+    # The bar here: every element within TWO bf16 steps of the oracle and all but 1e-4 of them within one, at most
+    # 2 % off at all, and the error of the whole tensor far below 1e-2 RMS in the root-mean-square sense.
     d = (y.float() - want.float()).abs()
-    step = torch.maximum(want.float().abs(), y.float().abs()).clamp_min(2.0 ** -126)
-    step = torch.exp2(torch.floor(torch.log2(step)) - 7)             # bf16 spacing at that magnitude
-    assert bool((d <= step).all()), f"an output is more than one bf16 step off (max {d.max().item()})"
+    # magnitude at which the roundings happened: the dequantised term, the LoRA term or their sum, whichever is largest
+    mag = torch.maximum(torch.maximum(base.float().abs(), (want.float() - base.float()).abs()), want.float().abs())
+    step = torch.exp2(torch.floor(torch.log2(mag.clamp_min(2.0 ** -126))) - 7)      # bf16 spacing at that magnitude
+    assert bool((d <= 2 * step).all()), f"an output is more than two bf16 steps off (max {d.max().item()})"
+    assert (d > step).float().mean().item() <= 1e-4
     assert (_bits(y) != _bits(want)).float().mean().item() <= 0.02
     assert float(d.double().pow(2).mean().sqrt()) <= 1e-3 * _rms(want.float())
     small = want.float().abs() < 4.0                                  # where a bf16 step is below 1e-2 RMS

@@ -454,6 +454,67 @@ def test_peer_barrier_meets_and_times_out_on_one_gpu(cuda_pkg):
         F.peer_barrier([mine.data_ptr()] * 9, 0, 1, dev)
 
 
+# ------------------------------------------------------------------ quantiser prologues
+@pytest.mark.parametrize("M,K,dt", [(64, 4096, torch.bfloat16), (33, 256, torch.bfloat16), (7, 1032, torch.float16),
+                                    (130, 12288, torch.bfloat16), (5, 16384, torch.float16), (1, 8, torch.bfloat16)])
+def test_ln_modulate_quantiser_bit_exact(cuda_pkg, M, K, dt):
+    """LayerNorm -> (1 + scale), shift -> per-token int8 in one kernel: int8, scales and the modulated activations
+    equal the bit-level definition; the same tensor built from PyTorch's own LayerNorm and addcmul agrees to within
+    a bf16 / fp16 step (its reductions run in another order)."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = (wl.activation(M, K, seed=50, dtype=torch.float32) * 0.7 + 0.3).to(dt)
+    g = torch.Generator().manual_seed(K + M)
+    shift = (torch.randn(K, generator=g) * 0.2).to(dt)
+    scale = (torch.randn(K, generator=g) * 0.3).to(dt)
+    q, rs, y = F.quantize_rowwise_ln_modulate(x.to(DEV), shift.to(DEV), scale.to(DEV), eps=1e-5, return_y=True)
+    q_want, s_want, y_want = bs.quantize_rowwise_ln_modulate(to_np(x), to_np(shift), to_np(scale), 1e-5, NAME[dt])
+    assert np.array_equal(to_np(y), y_want)
+    assert np.array_equal(to_np(rs), s_want) and np.array_equal(to_np(q), q_want)
+    q2, rs2 = F.quantize_rowwise_ln_modulate(x.to(DEV), shift.to(DEV), scale.to(DEV), eps=1e-5)
+    assert torch.equal(q2, q) and torch.equal(rs2, rs)
+    lib = torch.addcmul(shift.to(DEV), torch.nn.functional.layer_norm(x.to(DEV), (K,)), 1 + scale.to(DEV))
+    d = (y.float() - lib.float()).abs()
+    step = torch.exp2(torch.floor(torch.log2(lib.float().abs().clamp_min(2.0 ** -14))) - (7 if dt == torch.bfloat16 else 10))
+    assert bool((d <= 2 * step + 1e-3).all()) and (d > 0).float().mean().item() <= 0.05
+
+
+@pytest.mark.parametrize("M,K0,K1,dt", [(64, 0, 12288, torch.bfloat16), (40, 4096, 12288, torch.bfloat16), (9, 128, 264, torch.float16),
+                                        (3, 0, 8, torch.bfloat16), (130, 256, 768, torch.bfloat16)])
+def test_gelu_quantiser_bit_exact(cuda_pkg, M, K0, K1, dt):
+    """[ plain | GELU_tanh ] -> per-token int8 in one kernel, the two parts read as column slices of wider matrices."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    wide = (wl.activation(M, K1 + 64, seed=51, dtype=torch.float32) * 1.5).to(dt).to(DEV)
+    xg = wide[:, 64:]                                                 # a column slice, as in a fused qkv + mlp buffer
+    xp = (wl.activation(M, K0, seed=52, dtype=torch.float32)).to(dt).to(DEV) if K0 else None
+    q, rs, y = F.quantize_rowwise_gelu(xg, xp, return_y=True)
+    q_want, s_want, y_want = bs.quantize_rowwise_gelu(to_np(xg), None if xp is None else to_np(xp), NAME[dt])
+    assert np.array_equal(to_np(y), y_want)
+    assert np.array_equal(to_np(rs), s_want) and np.array_equal(to_np(q), q_want)
+    lib = torch.nn.functional.gelu(xg, approximate="tanh")
+    got = y[:, K0:]
+    d = (got.float() - lib.float()).abs()
+    step = torch.exp2(torch.floor(torch.log2(lib.float().abs().clamp_min(2.0 ** -14))) - (7 if dt == torch.bfloat16 else 10))
+    assert bool((d <= step + 1e-6).all()) and (d > 0).float().mean().item() <= 0.01
+    # special values: zero, large magnitudes of both signs
+    sp = torch.tensor([[0.0, -0.0, 30.0, -30.0, 1e4, -1e4, 1e-3, -1e-3]], dtype=dt, device=DEV)
+    _, _, ysp = F.quantize_rowwise_gelu(sp, None, return_y=True)
+    assert np.array_equal(to_np(ysp), bs.round_to(bs.gelu_tanh(to_np(sp)), NAME[dt]))
+    assert float(ysp[0, 2]) == 30.0 and abs(float(ysp[0, 3])) < 1e-30 and float(ysp[0, 4]) == float(sp[0, 4])
+
+
+@pytest.mark.parametrize("rows,cols,dt", [(70, 256, torch.bfloat16), (513, 1024, torch.float16), (1, 128, torch.bfloat16)])
+def test_rmsnorm_heads_bit_exact(cuda_pkg, rows, cols, dt):
+    """Per-head RMS norm in place over the q and k columns of a wider (qkv) buffer."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    buf = wl.activation(rows, cols + 128, seed=53, dtype=torch.float32).to(dt).to(DEV)
+    before = buf.clone()
+    F.rmsnorm_heads_(buf[:, :cols], eps=1e-6)
+    assert np.array_equal(to_np(buf[:, :cols]), bs.rmsnorm_heads(to_np(before[:, :cols]), 1e-6, NAME[dt]))
+    assert torch.equal(buf[:, cols:], before[:, cols:])                       # the v columns are untouched
+    lib = torch.nn.functional.rms_norm(before[:, :cols].reshape(rows, cols // 128, 128), (128,), eps=1e-6).reshape(rows, cols)
+    assert (buf[:, :cols] != lib).float().mean().item() <= 0.01
+
+
 # ------------------------------------------------------------------ tiny-batch branch (M <= 16)
 @pytest.mark.parametrize("M,K,N,per_channel,bias_dt,dt", [
     (1, 4096, 4096, False, torch.bfloat16, torch.bfloat16),     # a modulation-sized call

@@ -279,7 +279,7 @@ def test_synthetic_dit_step_small(cuda_pkg):
     dit = importlib.import_module(cuda_pkg.__name__ + ".dit")
     cfg = dit.DiTConfig(hidden=256, heads=2, mlp_ratio=3, double_blocks=1, single_blocks=2, img_tokens=64, txt_tokens=32,
                         in_channels=16, txt_dim=128)
-    model = dit.SyntheticDiT(cfg, seed=3, device=DEV)
+    model = dit.SyntheticDiT(cfg, seed=3, device=DEV, fused=False)     # every linear through its module call
     seen = []
     ops_cls = cuda_pkg.ops.StandaloneInt8Ops
     for m in model.modules():
@@ -296,6 +296,19 @@ def test_synthetic_dit_step_small(cuda_pkg):
     assert len(seen) == cfg.double_blocks * 8 + cfg.single_blocks * 2
     assert torch.equal(model(img, txt, t), y1)
     assert sum(p.numel() for m in model.modules() if isinstance(m, ops_cls.Linear) for p in [m.weight]) == cfg.int8_params()
+    # the fused block code (LayerNorm + modulation and GELU inside the quantiser, one qkv buffer, the per-head RMS-norm
+    # kernel) computes the same network: same weights, outputs equal up to the roundings that moved
+    fused = dit.SyntheticDiT(cfg, seed=3, device=DEV, fused=True)
+    nat = cuda_pkg._native
+    before = nat.load().i8f_launch_count()
+    y2 = fused(img, txt, t)
+    launched = nat.load().i8f_launch_count() - before
+    assert torch.equal(fused(img, txt, t), y2)
+    err = (y2.float() - y1.float()).abs().max().item()
+    assert err <= 3e-2 * y1.float().pow(2).mean().sqrt().item(), err
+    # per double block and stream: 2 LN-quantisers, 1 GELU-quantiser, 3 GEMMs, proj (quantiser + GEMM); one RMS norm
+    # per block; per single block: LN-quantiser, GEMM, RMS norm, GELU-quantiser, GEMM
+    assert launched == cfg.double_blocks * (2 * 8 + 1) + cfg.single_blocks * 5
 
 
 def test_linear_traces_under_torch_compile(cuda_pkg, ops):
