@@ -50,6 +50,8 @@ _PROTOTYPES = {
                                 c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "i8f_linear_w8a8_add": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
                                     c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "i8f_linear_w8a8_gated_add": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "i8f_linear_w8a8_lora": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int,
                                      c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
                                      c_int64, c_int, c_void_p]),

@@ -65,6 +65,7 @@ struct GemmParams {
     int epi_mode;
     int epi_order;
     int add_existing;  // dequant mode: out = round(round(result) + out) (a LoRA term already stored in out)
+    const void* gate;  // with add_existing: out = round(out + gate[n] * round(result)), gate [N] in the output type
     int vec_ok;  // out pointer / pitch allow 16-byte row-segment stores
     int tma_out; // 16-bit output leaves through shared memory and TMA stores (needs vec_ok)
     int lora_k_blocks;  // fused dynamic LoRA: 64-element slabs of the rank (0 = none)
@@ -257,7 +258,7 @@ template <int OUT, bool LORA>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long row, bool row_ok, int col,
                                                const uint32_t (&v)[32], const uint32_t (&lv)[LORA ? 32 : 1], float row_scale,
                                                float ws_scalar, const float* cs, const float* cb, const OldChunk& old,
-                                               uint32_t stage, int lane, int wide_half = -1) {
+                                               uint32_t stage, int lane, int wide_half = -1, const uint32_t* cg = nullptr) {
     uint32_t yp[16];
     if (p.epi_mode == kEpiDequant) {
         const bool per_ch = p.w_scale_mode == I8F_WSCALE_CHANNEL;
@@ -297,8 +298,19 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, long long ro
         if (p.add_existing && row_ok) {
             uint32_t prev[16];
             old_values<OUT>(p, row, col, old, prev);
+            if (cg != nullptr) {
+                // gated residual: prev + gate * y in fp32 (the product of two 16-bit values is exact, so the sum is
+                // rounded once), then to the output type -- what torch.addcmul(prev, gate, y) computes
 #pragma unroll
-            for (int i = 0; i < 16; ++i) yp[i] = add2<OUT>(yp[i], prev[i]);
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t g = cg[i];
+                    yp[i] = pack2<OUT>(__fmaf_rn(unpack_lo<OUT>(g), unpack_lo<OUT>(yp[i]), unpack_lo<OUT>(prev[i])),
+                                       __fmaf_rn(unpack_hi<OUT>(g), unpack_hi<OUT>(yp[i]), unpack_hi<OUT>(prev[i])));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) yp[i] = add2<OUT>(yp[i], prev[i]);
+            }
         }
     } else if (p.epi_mode == kEpiCast) {
 #pragma unroll
@@ -552,6 +564,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool dequant = p.epi_mode == kEpiDequant;
         const bool per_ch = dequant && p.w_scale_mode == I8F_WSCALE_CHANNEL;
         const bool has_bias = dequant && p.bias != nullptr;
+        const bool has_gate = dequant && p.add_existing && p.gate != nullptr;
         const int bias_step = p.epi_order == I8F_EPI_PYTORCH ? 16 : 32;   // packed pairs or fp32 per 32-column chunk
         const float ws_scalar = (dequant && !per_ch) ? __ldg(p.w_scale) : 0.f;
         const uint32_t accempty_leader = PAIR ? mapa_cluster(accempty0, 0) : accempty0;
@@ -564,13 +577,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int m_blk, n_blk;
             tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
             // stage this tile's column scales and biases (fp32) for broadcast reads
-            if (per_ch || has_bias) {
+            if (per_ch || has_bias || has_gate) {
                 __syncwarp();
                 for (int j = lane; j < BN; j += 32) {
                     const int col = n_blk * BN + j;
                     const bool in = col < p.N;
                     if (per_ch) col_scale[j] = in ? __ldg(p.w_scale + col) : 0.f;
                     if (has_bias && p.epi_order != I8F_EPI_PYTORCH) col_bias[j] = in ? load_as_f32(p.bias, p.bias_dtype, col) : 0.f;
+                }
+                if (has_gate) {
+                    // packed pairs in the upper half of the bias area (the reference order keeps its biases as packed
+                    // pairs in the lower half; the gated form exists for that order only)
+                    uint32_t* packed = reinterpret_cast<uint32_t*>(col_bias) + BN / 2;
+                    for (int j = lane; j < BN / 2; j += 32) {
+                        const int col = n_blk * BN + 2 * j;
+                        const float g0 = col < p.N ? load_as_f32(p.gate, p.out_dtype, col) : 0.f;
+                        const float g1 = col + 1 < p.N ? load_as_f32(p.gate, p.out_dtype, col + 1) : 0.f;
+                        packed[j] = p.out_dtype == I8F_BF16 ? pack2<I8F_BF16>(g0, g1) : pack2<I8F_F16>(g0, g1);
+                    }
                 }
                 if (has_bias && p.epi_order == I8F_EPI_PYTORCH) {
                     // the reference casts the bias to the output type and adds 16-bit tensors: keep it as packed pairs
@@ -644,10 +668,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (row_ok) store_i32_row32(p, row, col, v);
                 } else if (p.out_dtype == I8F_BF16) {
                     epilogue_chunk<I8F_BF16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                   col_bias + c * bias_step, old_cur, stage, lane, wide_half);
+                                                   col_bias + c * bias_step, old_cur, stage, lane, wide_half,
+                                                   has_gate ? reinterpret_cast<const uint32_t*>(col_bias) + BN / 2 + c * 16 : nullptr);
                 } else {
                     epilogue_chunk<I8F_F16, LORA>(p, row, row_ok, col, v, lv, row_scale, ws_scalar, col_scale + c * 32,
-                                                  col_bias + c * bias_step, old_cur, stage, lane, wide_half);
+                                                  col_bias + c * bias_step, old_cur, stage, lane, wide_half,
+                                                  has_gate ? reinterpret_cast<const uint32_t*>(col_bias) + BN / 2 + c * 16 : nullptr);
                 }
                 if (wide_out) {
                     if (wide_half == 1) {
@@ -1015,7 +1041,7 @@ int i8f_gemm_i8_i32(const int8_t* a, int64_t lda, const int8_t* w, int64_t ldw, 
 static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
                             const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, void* out,
                             int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order,
-                            int add_existing, void* stream, const Scatter* scatter = nullptr) {
+                            int add_existing, void* stream, const Scatter* scatter = nullptr, const void* gate = nullptr) {
     int rc = check_operands(a, lda, w, ldw, 1, M, N, K);
     if (rc != I8F_OK) return rc;
     I8F_REQUIRE(a_scale != nullptr && w_scale != nullptr, I8F_ERR_INVALID_ARG, "NULL scale pointer");
@@ -1038,6 +1064,7 @@ static int linear_w8a8_impl(const int8_t* a, int64_t lda, const float* a_scale, 
     p.epi_mode = kEpiDequant;
     p.epi_order = epilogue_order;
     p.add_existing = add_existing;
+    p.gate = gate;
     p.vec_ok = aligned16(out) && (ldo % 8 == 0);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -1056,6 +1083,14 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale, cons
                         int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream) {
     return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
                             epilogue_order, 1, stream);
+}
+
+int i8f_linear_w8a8_gated_add(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,
+                              const float* w_scale, int w_scale_mode, const void* bias, int bias_dtype, const void* gate,
+                              void* out, int out_dtype, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream) {
+    I8F_REQUIRE(gate != nullptr, I8F_ERR_INVALID_ARG, "gate is NULL");
+    return linear_w8a8_impl(a, lda, a_scale, w, ldw, w_scale, w_scale_mode, bias, bias_dtype, out, out_dtype, ldo, M, N, K,
+                            I8F_EPI_PYTORCH, 1, stream, nullptr, gate);
 }
 
 int i8f_linear_w8a8_lora(const int8_t* a, int64_t lda, const float* a_scale, const int8_t* w, int64_t ldw,

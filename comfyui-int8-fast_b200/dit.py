@@ -84,6 +84,11 @@ def int8_gemm(lin, q: Tensor, q_scale: Tensor, out: Tensor | None = None) -> Ten
     return F.linear_w8a8(q, q_scale, lin.weight, lin._scale_on(q.device), lin.bias, torch.bfloat16, out=out)
 
 
+def int8_gemm_gated_add_(lin, residual: Tensor, gate: Tensor, q: Tensor, q_scale: Tensor) -> Tensor:
+    """residual += gate * lin(...) inside the GEMM epilogue (in place; the arithmetic of torch.addcmul)."""
+    return F.linear_w8a8_gated_add_(residual, gate, q, q_scale, lin.weight, lin._scale_on(q.device), lin.bias)
+
+
 def attention_prenormed(qkv: Tensor, heads: int) -> Tensor:
     """qkv [T, 3*h] whose q and k columns are already RMS-normalised per head -> attention output [T, h]."""
     t, h3 = qkv.shape
@@ -140,7 +145,8 @@ class DoubleBlock(nn.Module):
     def forward_fused(self, img: Tensor, txt: Tensor, vec: Tensor):
         """The same block with the element-wise steps around the quantised linears folded into the library's kernels:
         LayerNorm + modulation and GELU run inside the activation quantiser, both streams' qkv projections write into
-        one buffer, and the per-head RMS norm of q and k is one in-place launch over it.  img [Ti, h], txt [Tt, h]."""
+        one buffer, the per-head RMS norm of q and k is one in-place launch over it, and the gated residual updates
+        happen in the GEMM epilogues.  img [Ti, h], txt [Tt, h]; both are updated in place and returned."""
         cfg = self.cfg
         h = cfg.hidden
         n_txt = txt.shape[0]
@@ -155,10 +161,10 @@ class DoubleBlock(nn.Module):
         outs = []
         for name, x, blk, a in (("txt", txt, self.txt, attn[:n_txt]), ("img", img, self.img, attn[n_txt:])):
             sh1, sc1, g1, sh2, sc2, g2 = mods[name]
-            x = torch.addcmul(x, g1, blk.proj(a))
+            int8_gemm_gated_add_(blk.proj, x, g1, *F.quantize_rowwise(a))          # x += g1 * proj(attention)
             q8, xs = F.quantize_rowwise_ln_modulate(x, sh2, sc2)
             q8, xs = F.quantize_rowwise_gelu(int8_gemm(blk.mlp_up, q8, xs))
-            x = torch.addcmul(x, g2, int8_gemm(blk.mlp_down, q8, xs))
+            int8_gemm_gated_add_(blk.mlp_down, x, g2, q8, xs)                         # x += g2 * mlp(...)
             outs.append(x)
         return outs[1], outs[0]
 
@@ -198,7 +204,7 @@ class SingleBlock(nn.Module):
         F.rmsnorm_heads_(y[:, : 2 * h])
         attn = attention_prenormed(y[:, : 3 * h], self.cfg.heads)
         q8, xs = F.quantize_rowwise_gelu(y[:, 3 * h:], attn)
-        return torch.addcmul(x, gate, int8_gemm(self.linear2, q8, xs))
+        return int8_gemm_gated_add_(self.linear2, x, gate, q8, xs)
 
     def forward(self, x: Tensor, vec: Tensor) -> Tensor:
         h = self.cfg.hidden

@@ -210,6 +210,32 @@ def linear_w8a8(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | N
     return out
 
 
+def linear_w8a8_gated_add_(residual: Tensor, gate: Tensor, q: Tensor, q_scale: Tensor, w: Tensor, w_scale,
+                           bias: Tensor | None) -> Tensor:
+    """In place residual <- round(residual + gate * round(dequant(q @ w^T) (+ bias))): the gated branch of a
+    transformer block added to its residual stream inside the GEMM epilogue (torch.addcmul's arithmetic).
+    residual [M,N] bf16 / fp16 with unit inner stride, gate [N]."""
+    nat.require_device(q.device)
+    q, w = _rows(q), _rows(w)
+    M, K = q.shape
+    N = w.shape[0]
+    _check_weight(w, K)
+    if residual.shape != (M, N) or residual.stride(1) != 1 or residual.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("residual must be [M,N] bf16 / fp16 with unit inner stride")
+    gate = gate.reshape(-1).to(device=q.device, dtype=residual.dtype).contiguous()
+    if gate.numel() != N:
+        raise ValueError(f"gate must have {N} elements")
+    ws, mode = _wscale_arg(w_scale, q.device, N)
+    if bias is not None:
+        bias = bias.to(q.device).contiguous()
+    if M and N:
+        nat.check(nat.load().i8f_linear_w8a8_gated_add(nat.ptr(q), _ld(q), nat.ptr(q_scale.reshape(-1)), nat.ptr(w), _ld(w),
+                                                       nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
+                                                       nat.ptr(gate), nat.ptr(residual), _code(residual.dtype), _ld(residual),
+                                                       M, N, K, nat.current_stream(q.device)), "i8f_linear_w8a8_gated_add")
+    return residual
+
+
 def linear_w8a8_lora(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Tensor | None, t: Tensor, lora_b: Tensor,
                      out_dtype: torch.dtype, order: int = nat.EPI_PYTORCH) -> Tensor:
     """Dequantising int8 GEMM with the dynamic-LoRA term round(t @ lora_b^T) added inside the kernel."""

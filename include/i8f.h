@@ -164,6 +164,17 @@ int i8f_linear_w8a8_add(const int8_t* a, int64_t lda, const float* a_scale,
                         void* out, int out_dtype, int64_t ldo,
                         int64_t M, int64_t N, int64_t K, int epilogue_order, void* stream);
 
+/* Gated residual update in the epilogue, in place:
+ *   out = round(out_before + gate[n] * round(dequant (+bias)))       (reference rounding order for the linear itself)
+ * gate [N] in out_dtype.  gate * y is exact in fp32, so the sum has one fp32 rounding before the rounding to
+ * out_dtype: the arithmetic of torch.addcmul(out_before, gate, linear(x)), which is how a diffusion transformer
+ * block adds a gated branch to its residual stream.  No counterpart in the reference (the model does this step). */
+int i8f_linear_w8a8_gated_add(const int8_t* a, int64_t lda, const float* a_scale,
+                              const int8_t* w, int64_t ldw, const float* w_scale, int w_scale_mode,
+                              const void* bias, int bias_dtype, const void* gate,
+                              void* out, int out_dtype, int64_t ldo,
+                              int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Quantised linear with the dynamic-LoRA term fused in:
  *   out = round(round(dequant (+bias)) + round(t [M,r] @ lora_b [N,r]^T))
  * t and lora_b are in out_dtype (bf16 or fp16), pitches multiples of 8 elements.  The low-rank product is

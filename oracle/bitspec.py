@@ -438,3 +438,10 @@ def rmsnorm_heads(x: np.ndarray, eps: float = 1e-6, dtype: str = "bf16") -> np.n
     ms = (s * F32(0.0078125) + F32(eps)).astype(F32)
     rstd = (F32(1.0) / np.sqrt(ms)).astype(F32)
     return round_to(x.reshape(rows, cols // 128, 128) * rstd, dtype).reshape(rows, cols)
+
+
+def gated_add(residual: np.ndarray, gate: np.ndarray, y: np.ndarray, dtype: str = "bf16") -> np.ndarray:
+    """rnd(residual + gate[n] * y): a gated branch added to the residual stream (torch.addcmul's arithmetic).  All
+    three operands hold values of the 16-bit type, so gate * y is exact in fp32 and the sum is rounded once."""
+    prod = np.asarray(gate, dtype=F32).reshape(1, -1).astype(np.float64) * np.asarray(y, dtype=F32).astype(np.float64)
+    return round_to((np.asarray(residual, dtype=F32).astype(np.float64) + prod).astype(F32), dtype)
