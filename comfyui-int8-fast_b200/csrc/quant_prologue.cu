@@ -281,6 +281,95 @@ gelu_quant_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, const vo
     quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
 }
 
+// The same quantiser for large inputs: a 16-bit activation has only 65536 possible values, so rnd(GELU(x)) is read from
+// a table (built once per device by gelu_table_kernel with the very arithmetic above, so the bits are the same) that
+// every CTA of a persistent grid keeps in shared memory.  One table look-up per element instead of some forty fp32
+// instructions, which left the direct kernel at a quarter of the memory rate.
+constexpr int kTableThreads = 512;
+__device__ unsigned short g_gelu_table[2][65536];      // [0] bf16, [1] fp16
+
+template <int DT>
+__global__ void gelu_table_kernel(unsigned short* __restrict__ table) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) return;
+    float x;
+    if constexpr (DT == I8F_BF16) x = __uint_as_float(i << 16);
+    else x = __half2float(__ushort_as_half(static_cast<unsigned short>(i)));
+    table[i] = static_cast<unsigned short>(pack2<DT>(gelu_tanh_exact(x), 0.f) & 0xFFFFu);
+}
+
+template <int DT, int VPT>
+__global__ void __launch_bounds__(kTableThreads)
+gelu_quant_table_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, const void* __restrict__ x1, int64_t K1,
+                        int64_t ld1, int64_t M, int8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale,
+                        void* __restrict__ y_out, int64_t ldy, const unsigned short* __restrict__ table) {
+    extern __shared__ __align__(16) unsigned short s_table[];
+    __shared__ float s_part[kTableThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    for (int i = threadIdx.x; i < 65536 / 8; i += kTableThreads)
+        reinterpret_cast<uint4*>(s_table)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+    __syncthreads();
+    const int t = threadIdx.x & (kThreadsPerRow - 1);
+    const int row_in_cta = threadIdx.x >> 7;
+    const int nvec0 = static_cast<int>(K0 >> 3);
+    const int nvec = nvec0 + static_cast<int>(K1 >> 3);
+    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * 4; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * 4) {
+        const int64_t row = row0 + row_in_cta;
+        const bool row_ok = row < M;
+        uint4 raw[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            raw[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (row_ok && vec < nvec0)
+                raw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x0) + row * ld0 + static_cast<int64_t>(vec) * 8));
+            else if (row_ok && vec < nvec)
+                raw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x1) + row * ld1 + static_cast<int64_t>(vec - nvec0) * 8));
+        }
+        auto look2 = [&](uint32_t w) -> uint32_t {
+            return static_cast<uint32_t>(s_table[w & 0xFFFFu]) | (static_cast<uint32_t>(s_table[w >> 16]) << 16);
+        };
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            if (row_ok && vec >= nvec0 && vec < nvec)
+                raw[i] = make_uint4(look2(raw[i].x), look2(raw[i].y), look2(raw[i].z), look2(raw[i].w));
+            if (y_out != nullptr && row_ok && vec < nvec)
+                *reinterpret_cast<uint4*>(static_cast<unsigned short*>(y_out) + row * ldy + static_cast<int64_t>(vec) * 8) = raw[i];
+        }
+        const float amax = row_max(packed_absmax<DT, VPT>(raw), s_part, row_in_cta);
+        quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
+    }
+}
+
+// Device address of the table for `dt` on the current device, built on `st` the first time it is asked for.  While
+// `st` is being captured into a graph the build is captured with it (and not remembered, since it has not run yet).
+int gelu_table(int dt, cudaStream_t st, const unsigned short** out) {
+    static unsigned short* base[64] = {nullptr};
+    static bool built[64][2] = {{false}};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(I8F_ERR_CUDA, "cudaGetDevice failed");
+    if (base[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_gelu_table);
+        if (e != cudaSuccess || p == nullptr) return fail(I8F_ERR_CUDA, "cudaGetSymbolAddress(GELU table): %s", cudaGetErrorString(e));
+        base[dev] = static_cast<unsigned short*>(p);
+    }
+    const int which = dt == I8F_BF16 ? 0 : 1;
+    unsigned short* table = base[dev] + which * 65536;
+    if (!built[dev][which]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cap);
+        if (which == 0) gelu_table_kernel<I8F_BF16><<<256, 256, 0, st>>>(table);
+        else gelu_table_kernel<I8F_F16><<<256, 256, 0, st>>>(table);
+        const int rc = check_launch("gelu_table_kernel");
+        if (rc != I8F_OK) return rc;
+        if (cap == cudaStreamCaptureStatusNone) built[dev][which] = true;
+    }
+    *out = table;
+    return I8F_OK;
+}
+
 // ------------------------------------------------------------------ per-head RMS norm, in place
 // Rows of `head_dim` = 128 elements (one attention head of one token): y = rnd(x * (1 / sqrt(sum(x^2) / 128 + eps))).
 // Sixteen lanes hold a head (8 elements each): squares summed sequentially per lane, then a butterfly over lane
@@ -383,8 +472,48 @@ int i8f_quant_rowwise_gelu(const void* x_plain, int64_t K0, int64_t ld0, const v
     rc = check_out(q, ldq, row_scale, K0 + K1, y_out, ldy);
     if (rc != I8F_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const unsigned grid = static_cast<unsigned>((M + 1) / 2);
     const int64_t nvec = (K0 + K1) / 8;
+    static const int table_mode = [] {      // I8F_GELU_TABLE = 0 never, 1 always, unset: by size
+        const char* e = getenv("I8F_GELU_TABLE");
+        return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+    }();
+    const bool use_table = table_mode == 1 || (table_mode == -1 && M * K1 >= (1 << 21));
+    if (use_table) {
+        // large inputs: persistent CTAs with the 128 KB look-up table in shared memory (same bits as the direct kernel)
+        const unsigned short* table = nullptr;
+        rc = gelu_table(x_dtype, st, &table);
+        if (rc != I8F_OK) return rc;
+        int sms = 148;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int64_t want = (M + 3) / 4;
+        const unsigned grid = static_cast<unsigned>(want < sms ? want : sms);
+        constexpr int kTableBytes = 65536 * 2;
+#define I8F_TABLE_GO(DT, V)                                                                                              \
+    do {                                                                                                                 \
+        auto kern = gelu_quant_table_kernel<DT, V>;                                                                      \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTableBytes);            \
+        if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));              \
+        kern<<<grid, kTableThreads, kTableBytes, st>>>(x_plain, K0, ld0, x_gelu, K1, ld1, M, q, ldq, row_scale, y_out,   \
+                                                      ldy, table);                                                       \
+    } while (0)
+        const int vpt = static_cast<int>((nvec + kThreadsPerRow - 1) / kThreadsPerRow);
+        if (x_dtype == I8F_BF16) {
+            if (vpt <= 4) I8F_TABLE_GO(I8F_BF16, 4);
+            else if (vpt <= 8) I8F_TABLE_GO(I8F_BF16, 8);
+            else if (vpt <= 12) I8F_TABLE_GO(I8F_BF16, 12);
+            else I8F_TABLE_GO(I8F_BF16, 16);
+        } else {
+            if (vpt <= 4) I8F_TABLE_GO(I8F_F16, 4);
+            else if (vpt <= 8) I8F_TABLE_GO(I8F_F16, 8);
+            else if (vpt <= 12) I8F_TABLE_GO(I8F_F16, 12);
+            else I8F_TABLE_GO(I8F_F16, 16);
+        }
+#undef I8F_TABLE_GO
+        return check_launch("gelu_quant_table_kernel");
+    }
+    const unsigned grid = static_cast<unsigned>((M + 1) / 2);
     if (x_dtype == I8F_BF16)
         I8F_DISPATCH_VPT(gelu_quant_kernel, I8F_BF16, nvec, x_plain, K0, ld0, x_gelu, K1, ld1, M, q, ldq, row_scale, y_out, ldy);
     else

@@ -94,13 +94,14 @@ def test_c2_dynamic_lora_full_size(cuda_pkg):
     # magnitude at which the roundings happened: the dequantised term, the LoRA term or their sum, whichever is largest
     mag = torch.maximum(torch.maximum(base.float().abs(), (want.float() - base.float()).abs()), want.float().abs())
     step = torch.exp2(torch.floor(torch.log2(mag.clamp_min(2.0 ** -126))) - 7)      # bf16 spacing at that magnitude
-    steps_off = d / step
-    stats = {"max_steps": steps_off.max().item(), "frac_gt2": (steps_off > 2).float().mean().item(),
-             "frac_gt1": (steps_off > 1).float().mean().item(), "frac_ne": (_bits(y) != _bits(want)).float().mean().item()}
     # t = x @ A^T is itself rounded to bf16 (steps of 0.125 at |t| ~ 16) before the up projection, whose result is
     # rounded again before the add: a chain of three roundings, each of which can move by one step between two
-    # correct implementations.  Almost all outputs agree exactly, a few are one or two steps apart, none more than four.
-    assert stats["max_steps"] <= 4 and stats["frac_gt2"] <= 1e-4 and stats["frac_gt1"] <= 2e-3 and stats["frac_ne"] <= 0.02, stats
+    # correct implementations.  Every output must meet the absolute bound 1e-2 RMS or, where bf16 itself is coarser
+    # than that, lie within two bf16 steps; almost all agree exactly.
+    within = (d <= TOL * _rms(want.float())) | (d <= 2 * step)
+    stats = {"max_abs_over_rms": d.max().item() / _rms(want.float()), "violations": int((~within).sum()),
+             "frac_ne": (_bits(y) != _bits(want)).float().mean().item()}
+    assert stats["violations"] == 0 and stats["frac_ne"] <= 0.02, stats
     assert float(d.double().pow(2).mean().sqrt()) <= 1e-3 * _rms(want.float())
     small = want.float().abs() < 4.0                                  # where a bf16 step is below 1e-2 RMS
     assert d[small].max().item() <= TOL * _rms(want.float())
