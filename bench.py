@@ -927,7 +927,10 @@ def column_parallel_record(pkg, rank, world, dev, dist, steps: int, m_sweep=(102
         ops = 2.0 * M * N * K
         comm_bytes = 2.0 * M * N * (world - 1) / world
         nvlink_ms = comm_bytes / (NVLINK_PEER_GBS * 1e9) * 1e3
-        rec = {"M": M, "ms_fused_epilogue_scatter": ms_fused, "ms_nccl_blocks_layout": ms_blocks,
+        compute_ms = (ops / world) / (2.0 * measured_peaks()[0]["bf16_tflops"] * 1e12) * 1e3   # this rank's slice of the GEMM
+        floor_ms = max(nvlink_ms, compute_ms)
+        rec = {"M": M, "compute_floor_ms": compute_ms, "roofline_ms": floor_ms, "frac_of_roofline_fused": floor_ms / ms_fused,
+               "ms_fused_epilogue_scatter": ms_fused, "ms_nccl_blocks_layout": ms_blocks,
                "ms_nccl_row_major_layout": ms_full, "fused_equals_nccl_result": bool(flags[0] == 1.0),
                "tops_fused": ops / (ms_fused * 1e-3) / 1e12, "allgather_bytes_in_per_gpu": comm_bytes,
                "nvlink_roofline_ms": nvlink_ms, "frac_of_nvlink_roofline_fused": nvlink_ms / ms_fused,
@@ -1234,12 +1237,76 @@ def run_small_batch(args):
                       "gpu_launches": steps * world, "clocks": clocks, "device_status": pkg._native.device_status()}))
 
 
+def run_prologue(args):
+    """The quantiser prologues and the per-head RMS norm alone, on the shapes of the synthetic DiT (4608 tokens): one
+    JSON line with the time and achieved HBM rate of each.  Inputs rotate over buffer sets larger than L2."""
+    import torch
+    import __graft_entry__ as g
+    rank, world, local_rank, dev, dist = rank_context()
+    pkg = g.load_package()
+    F = pkg.functional
+    T, h, m = 4608, 4096, 12288
+    n_sets = 4
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    xs_h = [torch.randn(T, h, generator=gen, device=dev).bfloat16() for _ in range(n_sets * 2)]       # 38 MB each
+    ys = [torch.randn(T, 3 * h + m, generator=gen, device=dev).bfloat16() for _ in range(n_sets)]      # 226 MB each
+    attn = [torch.randn(T, h, generator=gen, device=dev).bfloat16() for _ in range(n_sets)]
+    shift = (torch.randn(h, generator=gen, device=dev) * 0.1).bfloat16()
+    scale = (torch.randn(h, generator=gen, device=dev) * 0.1).bfloat16()
+    cases = {
+        "ln_modulate_quant_kernel [4608 x 4096]": (lambda i: F.quantize_rowwise_ln_modulate(xs_h[i % len(xs_h)], shift, scale), T * h * 3 + 4 * T + 4 * h),
+        "gelu_quant (table) [4608 x (4096 plain + 12288 GELU)]": (lambda i: F.quantize_rowwise_gelu(ys[i % n_sets][:, 3 * h:], attn[i % n_sets]), T * (h + m) * 3 + 4 * T),
+        "gelu_quant (table) [4608 x 12288]": (lambda i: F.quantize_rowwise_gelu(ys[i % n_sets][:, :m]), T * m * 3 + 4 * T),
+        "rmsnorm_heads_kernel [4608 x 8192 of a 24576-wide buffer]": (lambda i: F.rmsnorm_heads_(ys[i % n_sets][:, : 2 * h]), T * 2 * h * 4),
+        "quant_rows_kernel [4608 x 4096] (plain quantiser, for comparison)": (lambda i: F.quantize_rowwise(xs_h[i % len(xs_h)]), T * h * 3 + 4 * T),
+    }
+    peaks, kind = measured_peaks()
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        side = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(side):
+            for i in range(8):
+                fn(i)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(8):
+                    fn(i)
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(max(4, min(args.steps, 12))):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / 8)
+        ms = median(ts[1:])
+        out[name] = {"ms": ms, "algorithmic_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        del graph
+    if dist is not None:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    head = out["gelu_quant (table) [4608 x (4096 plain + 12288 GELU)]"]
+    print(json.dumps({"metric": "quantiser_prologue_bandwidth", "value": head["gbs"], "unit": "GB/s", "n_gpus": world,
+                      "steps": args.steps, "warmup": 8, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "dit_quantiser_prologues", "tokens": T, "hidden": h, "mlp_hidden": m,
+                                 "l2": "inputs rotate over 4 to 8 buffer sets (150 MB to 900 MB > 126 MB L2)"},
+                      "roofline": {"bound": "hbm", "kernel": "gelu_quant_table_kernel", "achieved": head["gbs"], "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": head["frac_of_hbm"], "traffic": None,
+                                   "peak_source": f"hbm_gbs of {kind} MEASURED_PEAKS.json; launches replayed from a CUDA graph of 8"},
+                      "kernels": out, "gpu_launches": 8 * len(cases), "device_status": pkg._native.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm", "prologue"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--dit-unfused", action="store_true",
                     help="dit: the block code without the fused quantiser prologues (every element-wise step a PyTorch call)")
@@ -1259,6 +1326,8 @@ def main():
         run_merge(args)
     elif args.workload == "smallm":
         run_small_batch(args)
+    elif args.workload == "prologue":
+        run_prologue(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

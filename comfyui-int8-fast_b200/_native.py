@@ -147,5 +147,11 @@ def ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def current_stream(device: torch.device) -> c_void_p:
+    """The current CUDA stream of `device` as a raw handle (the library enqueues on it and nowhere else)."""
+    if _raw_stream is not None:   # no Stream object is built: this call sits in front of every kernel launch
+        return c_void_p(_raw_stream(device.index if device.index is not None else torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream(device).cuda_stream)
