@@ -764,9 +764,43 @@ EncodeFn get_encode_fn() {
     return fn;
 }
 
+// Encoded tensor maps depend only on the address and the geometry, and a model calls the same layers with the same
+// buffers step after step (weights, a reused workspace, allocator-recycled outputs): a small per-thread cache saves
+// the driver call, about a microsecond per map, three maps per launch.
+struct MapKey {
+    const void* base;
+    int64_t rows, cols, ld;
+    int tag;        // operand: kind * 1024 + box rows; output: -1 narrow box, -2 wide box
+    int device;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && tag == o.tag && device == o.device;
+    }
+};
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool valid;
+};
+constexpr int kMapCacheSlots = 64;
+MapSlot* map_cache_slot(const MapKey& k) {
+    static thread_local MapSlot slots[kMapCacheSlots] = {};
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+    h = (h ^ (h >> 17)) * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(k.rows) * 31 + static_cast<uint64_t>(k.cols) * 131 +
+        static_cast<uint64_t>(k.ld) * 7 + static_cast<uint64_t>(k.tag + 8);
+    return &slots[(h >> 20) % kMapCacheSlots];
+}
+
+int current_device();
+
 // K-major [rows, k_elems] matrix, box = one 128-byte span of K x box_rows, 128-byte swizzle.
 int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, int64_t k_elems, int64_t ld_elems,
                      int box_rows) {
+    const MapKey key{base, rows, k_elems, ld_elems, kind * 1024 + box_rows, current_device()};
+    MapSlot* slot = map_cache_slot(key);
+    if (slot->valid && slot->key == key) {
+        *tm = slot->map;
+        return I8F_OK;
+    }
     EncodeFn enc = get_encode_fn();
     I8F_REQUIRE(enc != nullptr, I8F_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const int esz = kind == kKindI8 ? 1 : 2;
@@ -781,11 +815,20 @@ int make_operand_map(CUtensorMap* tm, int kind, const void* base, int64_t rows, 
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     I8F_REQUIRE(r == CUDA_SUCCESS, I8F_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    slot->key = key;
+    slot->map = *tm;
+    slot->valid = true;
     return I8F_OK;
 }
 
 // Output [rows, cols] of 16-bit elements, box = 32 columns x 32 rows (one epilogue warp's chunk), 64-byte swizzle.
 int make_out_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, int64_t ld_elems, bool wide = false) {
+    const MapKey key{base, rows, cols, ld_elems, wide ? -2 : -1, current_device()};
+    MapSlot* slot = map_cache_slot(key);
+    if (slot->valid && slot->key == key) {
+        *tm = slot->map;
+        return I8F_OK;
+    }
     EncodeFn enc = get_encode_fn();
     I8F_REQUIRE(enc != nullptr, I8F_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -797,6 +840,9 @@ int make_out_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t cols, 
                            CU_TENSOR_MAP_L2_PROMOTION_NONE,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     I8F_REQUIRE(r == CUDA_SUCCESS, I8F_ERR_CUDA, "cuTensorMapEncodeTiled(out) failed with CUresult %d", static_cast<int>(r));
+    slot->key = key;
+    slot->map = *tm;
+    slot->valid = true;
     return I8F_OK;
 }
 

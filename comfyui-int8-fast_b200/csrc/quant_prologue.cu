@@ -212,6 +212,99 @@ ln_modulate_quant_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64
     quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
 }
 
+// The same arithmetic for rows of at most 4096 elements (the hidden size of the transformer, where this kernel runs):
+// a persistent grid whose threads keep their columns' shift and rnd(1 + scale) as fp32 in registers across rows, and
+// the row itself as fp32 between the three passes (mean, variance, output) instead of re-widening it each time.
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2)
+ln_modulate_quant_fast_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const void* __restrict__ shift,
+                              const void* __restrict__ mscale, float eps, int8_t* __restrict__ q, int64_t ldq,
+                              float* __restrict__ scale, void* __restrict__ y_out, int64_t ldy) {
+    constexpr int VPT = 4;
+    __shared__ float s_part[kThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int t = threadIdx.x & (kThreadsPerRow - 1);
+    const int row_in_cta = threadIdx.x >> 7;
+    const int nvec = static_cast<int>(K >> 3);
+    const float kf = static_cast<float>(K);
+    float c_shift[VPT][8], c_gain[VPT][8];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int vec = i * kThreadsPerRow + t;
+        if (vec < nvec) {
+            float ms[8];
+            unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(shift) + static_cast<int64_t>(vec) * 8)), c_shift[i]);
+            unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(mscale) + static_cast<int64_t>(vec) * 8)), ms);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c_gain[i][j] = round_to_dt<DT>(__fadd_rn(1.0f, ms[j]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c_shift[i][j] = c_gain[i][j] = 0.f;
+        }
+    }
+    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * 2; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * 2) {
+        const int64_t row = row0 + row_in_cta;
+        const bool row_ok = row < M;
+        float v[VPT][8];
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            const uint4 r = (row_ok && vec < nvec)
+                                ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx + static_cast<int64_t>(vec) * 8))
+                                : make_uint4(0u, 0u, 0u, 0u);
+            unpack8<DT>(r, v[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const float s = seq_sum8(v[i]);
+            part = (i == 0) ? s : __fadd_rn(part, s);
+        }
+        const float mean = __fdiv_rn(row_sum(part, s_part, row_in_cta), kf);
+        part = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            float sq[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[i][j] = (vec < nvec) ? __fsub_rn(v[i][j], mean) : 0.f;      // the row is kept as deviations from here on
+                sq[j] = __fmul_rn(v[i][j], v[i][j]);
+            }
+            const float s = seq_sum8(sq);
+            part = (i == 0) ? s : __fadd_rn(part, s);
+        }
+        const float var = __fdiv_rn(row_sum(part, s_part, row_in_cta), kf);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+        uint4 raw[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // rnd((x - mean) * rstd) for a pair, then the modulation in fp32 and the rounding of its result
+                const uint32_t ln2 = pack2<DT>(__fmul_rn(v[i][2 * j], rstd), __fmul_rn(v[i][2 * j + 1], rstd));
+                float lo, hi;
+                if constexpr (DT == I8F_BF16) {
+                    lo = __uint_as_float(ln2 << 16);
+                    hi = __uint_as_float(ln2 & 0xFFFF0000u);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ln2));
+                    lo = f.x;
+                    hi = f.y;
+                }
+                w[j] = pack2<DT>(__fmaf_rn(lo, c_gain[i][2 * j], c_shift[i][2 * j]), __fmaf_rn(hi, c_gain[i][2 * j + 1], c_shift[i][2 * j + 1]));
+            }
+            raw[i] = (vec < nvec) ? make_uint4(w[0], w[1], w[2], w[3]) : make_uint4(0u, 0u, 0u, 0u);
+            if (y_out != nullptr && row_ok && vec < nvec)
+                *reinterpret_cast<uint4*>(static_cast<unsigned short*>(y_out) + row * ldy + static_cast<int64_t>(vec) * 8) = raw[i];
+        }
+        const float amax = row_max(packed_absmax<DT, VPT>(raw), s_part, row_in_cta);
+        quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
+    }
+}
+
 // ------------------------------------------------------------------ [ plain | GELU(tanh) ] -> int8
 // GELU in its tanh form, written as x * sigmoid(2u), u = x * (c0 + c1 * x^2), with the exponential spelled out in
 // correctly rounded fp32 operations only (no fused multiply-add, no approximate unit):
@@ -448,8 +541,22 @@ int i8f_quant_rowwise_ln_modulate(const void* x, int x_dtype, int64_t M, int64_t
     rc = check_out(q, ldq, row_scale, K, y_out, ldy);
     if (rc != I8F_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const unsigned grid = static_cast<unsigned>((M + 1) / 2);
     const int64_t nvec = K / 8;
+    static const int fast_ok = [] { const char* e = getenv("I8F_LN_FAST"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
+    if (fast_ok && nvec <= 4 * kThreadsPerRow) {
+        // rows of at most 4096 elements: persistent CTAs with the per-column constants in registers (same bits)
+        int sms = 148, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int64_t want = (M + 1) / 2;
+        const unsigned grid_p = static_cast<unsigned>(want < 4LL * sms ? want : 4LL * sms);
+        if (x_dtype == I8F_BF16)
+            ln_modulate_quant_fast_kernel<I8F_BF16><<<grid_p, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
+        else
+            ln_modulate_quant_fast_kernel<I8F_F16><<<grid_p, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
+        return check_launch("ln_modulate_quant_fast_kernel");
+    }
+    const unsigned grid = static_cast<unsigned>((M + 1) / 2);
     if (x_dtype == I8F_BF16)
         I8F_DISPATCH_VPT(ln_modulate_quant_kernel, I8F_BF16, nvec, x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
     else
