@@ -74,13 +74,18 @@ __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, f
 
 // Sum over the 128 threads of a row of one value per thread, in the fixed order of the header.  `s_part` has one
 // float per warp of the CTA; two barriers per call.
+// Barrier among the 128 threads (four warps) of one row only: the rows of a CTA run independently of each other, so
+// that one row's loads are in flight while another row computes.
+__device__ __forceinline__ void row_barrier(int row_in_cta) {
+    asm volatile("bar.sync %0, 128;" ::"r"(row_in_cta + 1) : "memory");
+}
 __device__ __forceinline__ float row_sum(float v, float* s_part, int row_in_cta) {
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
     const int warp = threadIdx.x >> 5;
-    __syncthreads();                       // previous use of s_part is over
+    row_barrier(row_in_cta);               // previous use of this row's slots of s_part is over
     if ((threadIdx.x & 31) == 0) s_part[warp] = v;
-    __syncthreads();
+    row_barrier(row_in_cta);
     const float* w = s_part + row_in_cta * 4;
     return __fadd_rn(__fadd_rn(__fadd_rn(w[0], w[1]), w[2]), w[3]);
 }
@@ -88,9 +93,9 @@ __device__ __forceinline__ float row_max(float v, float* s_part, int row_in_cta)
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
     const int warp = threadIdx.x >> 5;
-    __syncthreads();
+    row_barrier(row_in_cta);
     if ((threadIdx.x & 31) == 0) s_part[warp] = v;
-    __syncthreads();
+    row_barrier(row_in_cta);
     const float* w = s_part + row_in_cta * 4;
     return fmaxf(fmaxf(w[0], w[1]), fmaxf(w[2], w[3]));
 }
@@ -242,19 +247,25 @@ ln_modulate_quant_fast_kernel(const void* __restrict__ x, int64_t M, int64_t K, 
             for (int j = 0; j < 8; ++j) c_shift[i][j] = c_gain[i][j] = 0.f;
         }
     }
+    auto load_row = [&](int64_t row, uint4 (&dst)[VPT]) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * kThreadsPerRow + t;
+            dst[i] = (row < M && vec < nvec)
+                         ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx + static_cast<int64_t>(vec) * 8))
+                         : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    uint4 next[VPT];
+    load_row(static_cast<int64_t>(blockIdx.x) * 2 + row_in_cta, next);
     for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * 2; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * 2) {
         const int64_t row = row0 + row_in_cta;
         const bool row_ok = row < M;
         float v[VPT][8];
         float part = 0.f;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vec = i * kThreadsPerRow + t;
-            const uint4 r = (row_ok && vec < nvec)
-                                ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx + static_cast<int64_t>(vec) * 8))
-                                : make_uint4(0u, 0u, 0u, 0u);
-            unpack8<DT>(r, v[i]);
-        }
+        for (int i = 0; i < VPT; ++i) unpack8<DT>(next[i], v[i]);
+        load_row(row + static_cast<int64_t>(gridDim.x) * 2, next);      // the next row's loads fly under this row's arithmetic
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const float s = seq_sum8(v[i]);
