@@ -57,7 +57,18 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, const P
     }
     return make_uint4(x0, x1, x2, x3);
 }
-__device__ __forceinline__ float u01(uint32_t w) { return static_cast<float>(w >> 8) * 5.9604644775390625e-8f; }
+// Uniform in [0, 1) from 16 random bits: exactly representable, below 1.  One Philox block (four 32-bit words) thus
+// serves EIGHT weights; the generator is the largest single cost of the merge, and 2^-16 is far below the resolution
+// at which a rounding probability matters for weights that move by whole int8 steps.
+__device__ __forceinline__ float u01_16(uint32_t h) { return static_cast<float>(h) * 1.52587890625e-5f; }
+__device__ __forceinline__ void uniforms8(const uint4& r, float (&u)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        u[2 * i] = u01_16(w[i] & 0xFFFFu);
+        u[2 * i + 1] = u01_16(w[i] >> 16);
+    }
+}
 
 // floor(x/ws) + [u < frac], clamped to int8 range.  The IEEE division, floorf and the float->int conversion are
 // kept on purpose: a reciprocal-and-correct division and a magic-number floor were measured 1 - 3 % SLOWER here,
@@ -157,10 +168,7 @@ __device__ __forceinline__ void merge_tail(float (&acc)[2][8], int8_t* __restric
 #pragma unroll
             for (int c = 0; c < 8; ++c) u[c] = (kc + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + kc + c) : 1.f;
         } else {
-            const uint4 ra = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2), keys);
-            const uint4 rb = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 2) + 1u, keys);
-            u[0] = u01(ra.x); u[1] = u01(ra.y); u[2] = u01(ra.z); u[3] = u01(ra.w);
-            u[4] = u01(rb.x); u[5] = u01(rb.y); u[6] = u01(rb.z); u[7] = u01(rb.w);
+            uniforms8(philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kc >> 3), keys), u);
         }
         int8_t* wp = w + static_cast<long long>(n) * ldw + kc;
         if (pf.vec[i]) {
@@ -361,29 +369,28 @@ lora_merge_tc_kernel(int8_t* __restrict__ w, long long ldw, const float* __restr
 }
 
 // Element-wise stochastic rounding of an fp32 delta; one thread per group of
-// four columns (one Philox block).
+// eight columns (one Philox block).
 __global__ void __launch_bounds__(kThreads)
 stochastic_round_kernel(const float* __restrict__ delta, long long ldd, const float* __restrict__ w_scale, int ws_mode,
                         int8_t* __restrict__ d8, long long ldq, int N, int K, const float* __restrict__ uniforms,
                         const __grid_constant__ PhiloxKeys keys) {
-    const int groups = (K + 3) >> 2;
+    const int groups = (K + 7) >> 3;
     const long long total = static_cast<long long>(N) * groups;
     for (long long g = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; g < total;
          g += static_cast<long long>(gridDim.x) * kThreads) {
         const int n = static_cast<int>(g / groups);
         const int kg = static_cast<int>(g - static_cast<long long>(n) * groups);
         const float ws = ws_mode == I8F_WSCALE_CHANNEL ? __ldg(w_scale + n) : __ldg(w_scale);
-        float u[4];
+        float u[8];
         if (uniforms != nullptr) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) u[c] = (4 * kg + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + 4 * kg + c) : 1.f;
+            for (int c = 0; c < 8; ++c) u[c] = (8 * kg + c < K) ? __ldg(uniforms + static_cast<long long>(n) * K + 8 * kg + c) : 1.f;
         } else {
-            const uint4 rr = philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kg), keys);
-            u[0] = u01(rr.x); u[1] = u01(rr.y); u[2] = u01(rr.z); u[3] = u01(rr.w);
+            uniforms8(philox4x32_10(static_cast<uint32_t>(n), static_cast<uint32_t>(kg), keys), u);
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int k = 4 * kg + c;
+        for (int c = 0; c < 8; ++c) {
+            const int k = 8 * kg + c;
             if (k < K) d8[static_cast<long long>(n) * ldq + k] = static_cast<int8_t>(sr_round(__ldg(delta + static_cast<long long>(n) * ldd + k), ws, u[c]));
         }
     }
@@ -483,7 +490,7 @@ int i8f_stochastic_round(const float* delta, int64_t ldd, const float* w_scale, 
     I8F_REQUIRE(w_scale_mode == I8F_WSCALE_TENSOR || w_scale_mode == I8F_WSCALE_CHANNEL, I8F_ERR_INVALID_ARG,
                 "unknown w_scale_mode %d", w_scale_mode);
     I8F_REQUIRE(N < (1LL << 31) && K < (1LL << 31), I8F_ERR_UNSUPPORTED, "dimension too large");
-    const long long total = N * ((K + 3) / 4);
+    const long long total = N * ((K + 7) / 8);
     long long blocks = (total + kThreads - 1) / kThreads;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
     stochastic_round_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(

@@ -41,6 +41,27 @@ __device__ __forceinline__ void unpack8(const uint4& r, float (&v)[8]) {
         }
     }
 }
+// The same widening, but opaque to the optimiser: a kernel that walks its packed row several times would otherwise
+// keep all the widened values alive between the passes (twice the registers, half the occupancy).
+template <int DT>
+__device__ __forceinline__ void unpack8_again(const uint4& r, float (&v)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (DT == I8F_BF16) {
+            uint32_t lo, hi;
+            asm volatile("shl.b32 %0, %2, 16;\n\tand.b32 %1, %2, 0xFFFF0000;" : "=r"(lo), "=r"(hi) : "r"(w[i]));
+            v[2 * i] = __uint_as_float(lo);
+            v[2 * i + 1] = __uint_as_float(hi);
+        } else {
+            uint32_t x;
+            asm volatile("mov.b32 %0, %1;" : "=r"(x) : "r"(w[i]));
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+}
 template <int DT>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     if constexpr (DT == I8F_BF16) {
@@ -146,8 +167,9 @@ __device__ __forceinline__ void quantise_and_store(const uint4 (&raw)[VPT], floa
 // ------------------------------------------------------------------ LayerNorm * (1 + scale) + shift -> int8
 //   mean = rowsum(x) / K                     var = rowsum((x - mean)^2) / K         rstd = 1 / sqrt(var + eps)
 //   ln   = rnd((x - mean) * rstd)            y = rnd(ln * rnd(1 + scale[k]) + shift[k])      (rnd: to the 16-bit type)
-// ln * rnd(1 + scale) is exact in fp32 (two 16-bit significands), so the last line has a single fp32 rounding
-// before rnd.  Then q = rint(y * (1 / s)), s = max(absmax(y) / 127, 1e-30), as in the plain quantiser.
+// The last line is ONE rounding of the exact value ln * gain + shift to the 16-bit type (a fused multiply-add in that
+// type).  Then q = rint(y * (1 / s)), s = max(absmax(y) / 127, 1e-30), as in the plain quantiser.
+// This kernel (128 threads per row, sums in the order of the file header) serves rows longer than 4096 elements.
 template <int DT, int VPT>
 __global__ void __launch_bounds__(kThreads)
 ln_modulate_quant_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const void* __restrict__ shift,
@@ -202,13 +224,24 @@ ln_modulate_quant_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64
             unpack8<DT>(raw[i], f);
             unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(shift) + static_cast<int64_t>(vec) * 8)), sh);
             unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(mscale) + static_cast<int64_t>(vec) * 8)), ms);
+            uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float ln = round_to_dt<DT>(__fmul_rn(__fsub_rn(f[j], mean), rstd));
-                const float one_plus = round_to_dt<DT>(__fadd_rn(1.0f, ms[j]));
-                f[j] = __fmaf_rn(ln, one_plus, sh[j]);
+            for (int j = 0; j < 4; ++j) {
+                // rnd(ln * rnd(1 + scale) + shift): one fused multiply-add in the 16-bit type (exact value, one rounding)
+                const uint32_t ln2 = pack2<DT>(__fmul_rn(__fsub_rn(f[2 * j], mean), rstd), __fmul_rn(__fsub_rn(f[2 * j + 1], mean), rstd));
+                const uint32_t gain2 = pack2<DT>(__fadd_rn(1.0f, ms[2 * j]), __fadd_rn(1.0f, ms[2 * j + 1]));
+                const uint32_t sh2 = pack2<DT>(sh[2 * j], sh[2 * j + 1]);
+                if constexpr (DT == I8F_BF16) {
+                    const __nv_bfloat162 y = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&ln2), *reinterpret_cast<const __nv_bfloat162*>(&gain2),
+                                                     *reinterpret_cast<const __nv_bfloat162*>(&sh2));
+                    w[j] = *reinterpret_cast<const uint32_t*>(&y);
+                } else {
+                    const __half2 y = __hfma2(*reinterpret_cast<const __half2*>(&ln2), *reinterpret_cast<const __half2*>(&gain2),
+                                              *reinterpret_cast<const __half2*>(&sh2));
+                    w[j] = *reinterpret_cast<const uint32_t*>(&y);
+                }
             }
-            raw[i] = make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]), pack2<DT>(f[6], f[7]));
+            raw[i] = make_uint4(w[0], w[1], w[2], w[3]);
             if (y_out != nullptr && row_ok)
                 *reinterpret_cast<uint4*>(static_cast<unsigned short*>(y_out) + row * ldy + static_cast<int64_t>(vec) * 8) = raw[i];
         }
@@ -217,102 +250,115 @@ ln_modulate_quant_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64
     quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
 }
 
-// The same arithmetic for rows of at most 4096 elements (the hidden size of the transformer, where this kernel runs):
-// a persistent grid whose threads keep their columns' shift and rnd(1 + scale) as fp32 in registers across rows, and
-// the row itself as fp32 between the three passes (mean, variance, output) instead of re-widening it each time.
+// Rows of at most 4096 elements (the hidden size of the transformer, where this kernel runs) belong to ONE WARP: lane l
+// holds the vectors l, l + 32, ..., packed as loaded, so the three row reductions are shuffle butterflies with no
+// shared memory and no barrier, and the eight rows of a CTA proceed independently.  Order of a row sum here: the 8
+// elements of a vector left to right; a lane's vector sums in slot order; the 32 lanes as a balanced binary tree.
+// The modulation is one fused multiply-add per pair in the 16-bit type: rnd(ln * rnd(1 + scale) + shift) with a single
+// rounding of the exact value.
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 2)
-ln_modulate_quant_fast_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const void* __restrict__ shift,
+ln_modulate_quant_warp_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const void* __restrict__ shift,
                               const void* __restrict__ mscale, float eps, int8_t* __restrict__ q, int64_t ldq,
                               float* __restrict__ scale, void* __restrict__ y_out, int64_t ldy) {
-    constexpr int VPT = 4;
-    __shared__ float s_part[kThreads / 32];
+    constexpr int VPL = 16;     // vectors per lane: 32 lanes x 16 x 8 = 4096 elements
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int t = threadIdx.x & (kThreadsPerRow - 1);
-    const int row_in_cta = threadIdx.x >> 7;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    if (row >= M) return;                      // whole warps leave together; nothing below synchronises across warps
     const int nvec = static_cast<int>(K >> 3);
     const float kf = static_cast<float>(K);
-    float c_shift[VPT][8], c_gain[VPT][8];
+    uint4 raw[VPL];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int vec = i * kThreadsPerRow + t;
-        if (vec < nvec) {
-            float ms[8];
-            unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(shift) + static_cast<int64_t>(vec) * 8)), c_shift[i]);
-            unpack8<DT>(__ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(mscale) + static_cast<int64_t>(vec) * 8)), ms);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) c_gain[i][j] = round_to_dt<DT>(__fadd_rn(1.0f, ms[j]));
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) c_shift[i][j] = c_gain[i][j] = 0.f;
-        }
+    for (int i = 0; i < VPL; ++i) {
+        const int vec = i * 32 + lane;
+        raw[i] = vec < nvec ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx + static_cast<int64_t>(vec) * 8))
+                            : make_uint4(0u, 0u, 0u, 0u);
     }
-    auto load_row = [&](int64_t row, uint4 (&dst)[VPT]) {
+    auto warp_sum = [](float v) {
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vec = i * kThreadsPerRow + t;
-            dst[i] = (row < M && vec < nvec)
-                         ? __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x) + row * ldx + static_cast<int64_t>(vec) * 8))
-                         : make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int d = 1; d < 32; d <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+        return v;
     };
-    uint4 next[VPT];
-    load_row(static_cast<int64_t>(blockIdx.x) * 2 + row_in_cta, next);
-    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * 2; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * 2) {
-        const int64_t row = row0 + row_in_cta;
-        const bool row_ok = row < M;
-        float v[VPT][8];
-        float part = 0.f;
+    float part = 0.f;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) unpack8<DT>(next[i], v[i]);
-        load_row(row + static_cast<int64_t>(gridDim.x) * 2, next);      // the next row's loads fly under this row's arithmetic
+    for (int i = 0; i < VPL; ++i) {
+        float f[8];
+        unpack8_again<DT>(raw[i], f);
+        const float sv = seq_sum8(f);
+        part = (i == 0) ? sv : __fadd_rn(part, sv);
+    }
+    const float mean = __fdiv_rn(warp_sum(part), kf);
+    part = 0.f;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const float s = seq_sum8(v[i]);
-            part = (i == 0) ? s : __fadd_rn(part, s);
+    for (int i = 0; i < VPL; ++i) {
+        const int vec = i * 32 + lane;
+        float f[8];
+        unpack8_again<DT>(raw[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float d = (vec < nvec) ? __fsub_rn(f[j], mean) : 0.f;
+            f[j] = __fmul_rn(d, d);
         }
-        const float mean = __fdiv_rn(row_sum(part, s_part, row_in_cta), kf);
-        part = 0.f;
+        const float sv = seq_sum8(f);
+        part = (i == 0) ? sv : __fadd_rn(part, sv);
+    }
+    const float var = __fdiv_rn(warp_sum(part), kf);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+    uint32_t m2 = 0u;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vec = i * kThreadsPerRow + t;
-            float sq[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[i][j] = (vec < nvec) ? __fsub_rn(v[i][j], mean) : 0.f;      // the row is kept as deviations from here on
-                sq[j] = __fmul_rn(v[i][j], v[i][j]);
-            }
-            const float s = seq_sum8(sq);
-            part = (i == 0) ? s : __fadd_rn(part, s);
-        }
-        const float var = __fdiv_rn(row_sum(part, s_part, row_in_cta), kf);
-        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
-        uint4 raw[VPT];
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vec = i * kThreadsPerRow + t;
+    for (int i = 0; i < VPL; ++i) {
+        const int vec = i * 32 + lane;
+        if (vec < nvec) {
+            float f[8];
+            unpack8_again<DT>(raw[i], f);
+            const uint4 sh = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(shift) + static_cast<int64_t>(vec) * 8));
+            const uint4 ms = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(mscale) + static_cast<int64_t>(vec) * 8));
+            const uint32_t shw[4] = {sh.x, sh.y, sh.z, sh.w}, msw[4] = {ms.x, ms.y, ms.z, ms.w};
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                // rnd((x - mean) * rstd) for a pair, then the modulation in fp32 and the rounding of its result
-                const uint32_t ln2 = pack2<DT>(__fmul_rn(v[i][2 * j], rstd), __fmul_rn(v[i][2 * j + 1], rstd));
-                float lo, hi;
+                const uint32_t ln2 = pack2<DT>(__fmul_rn(__fsub_rn(f[2 * j], mean), rstd), __fmul_rn(__fsub_rn(f[2 * j + 1], mean), rstd));
                 if constexpr (DT == I8F_BF16) {
-                    lo = __uint_as_float(ln2 << 16);
-                    hi = __uint_as_float(ln2 & 0xFFFF0000u);
+                    const __nv_bfloat162 one = __floats2bfloat162_rn(1.0f, 1.0f);
+                    const __nv_bfloat162 gain = __hadd2(one, *reinterpret_cast<const __nv_bfloat162*>(&msw[j]));
+                    const __nv_bfloat162 y = __hfma2(*reinterpret_cast<const __nv_bfloat162*>(&ln2), gain, *reinterpret_cast<const __nv_bfloat162*>(&shw[j]));
+                    w[j] = *reinterpret_cast<const uint32_t*>(&y);
                 } else {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ln2));
-                    lo = f.x;
-                    hi = f.y;
+                    const __half2 one = __floats2half2_rn(1.0f, 1.0f);
+                    const __half2 gain = __hadd2(one, *reinterpret_cast<const __half2*>(&msw[j]));
+                    const __half2 y = __hfma2(*reinterpret_cast<const __half2*>(&ln2), gain, *reinterpret_cast<const __half2*>(&shw[j]));
+                    w[j] = *reinterpret_cast<const uint32_t*>(&y);
                 }
-                w[j] = pack2<DT>(__fmaf_rn(lo, c_gain[i][2 * j], c_shift[i][2 * j]), __fmaf_rn(hi, c_gain[i][2 * j + 1], c_shift[i][2 * j + 1]));
+                m2 = __vmaxu2(m2, w[j] & 0x7FFF7FFFu);
             }
-            raw[i] = (vec < nvec) ? make_uint4(w[0], w[1], w[2], w[3]) : make_uint4(0u, 0u, 0u, 0u);
-            if (y_out != nullptr && row_ok && vec < nvec)
+            raw[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            if (y_out != nullptr)
                 *reinterpret_cast<uint4*>(static_cast<unsigned short*>(y_out) + row * ldy + static_cast<int64_t>(vec) * 8) = raw[i];
+        } else {
+            raw[i] = make_uint4(0u, 0u, 0u, 0u);
         }
-        const float amax = row_max(packed_absmax<DT, VPT>(raw), s_part, row_in_cta);
-        quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
+    }
+    const uint32_t m16 = max(m2 & 0xFFFFu, m2 >> 16);
+    float amax;
+    if constexpr (DT == I8F_BF16) amax = __uint_as_float(m16 << 16);
+    else amax = __half2float(__ushort_as_half(static_cast<unsigned short>(m16)));
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+    const float sc = fmaxf(__fdiv_rn(amax, 127.0f), kScaleFloor);
+    const float inv = __fdiv_rn(1.0f, sc);
+    if (lane == 0) scale[row] = sc;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int vec = i * 32 + lane;
+        if (vec < nvec) {
+            float f[8];
+            unpack8_again<DT>(raw[i], f);
+            uint2 o;
+            o.x = quant4(f[0], f[1], f[2], f[3], inv);
+            o.y = quant4(f[4], f[5], f[6], f[7], inv);
+            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = o;
+        }
     }
 }
 
@@ -389,7 +435,7 @@ gelu_quant_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, const vo
 // a table (built once per device by gelu_table_kernel with the very arithmetic above, so the bits are the same) that
 // every CTA of a persistent grid keeps in shared memory.  One table look-up per element instead of some forty fp32
 // instructions, which left the direct kernel at a quarter of the memory rate.
-constexpr int kTableThreads = 512;
+constexpr int kTableThreads = 384;     // three rows at a time; 170 registers per thread leave room for the prefetched row
 __device__ unsigned short g_gelu_table[2][65536];      // [0] bf16, [1] fp16
 
 template <int DT>
@@ -407,29 +453,35 @@ __global__ void __launch_bounds__(kTableThreads)
 gelu_quant_table_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, const void* __restrict__ x1, int64_t K1,
                         int64_t ld1, int64_t M, int8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale,
                         void* __restrict__ y_out, int64_t ldy, const unsigned short* __restrict__ table) {
+    constexpr int kRows = kTableThreads / kThreadsPerRow;      // rows a CTA works on at a time
     extern __shared__ __align__(16) unsigned short s_table[];
     __shared__ float s_part[kTableThreads / 32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    for (int i = threadIdx.x; i < 65536 / 8; i += kTableThreads)
-        reinterpret_cast<uint4*>(s_table)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
-    __syncthreads();
     const int t = threadIdx.x & (kThreadsPerRow - 1);
     const int row_in_cta = threadIdx.x >> 7;
     const int nvec0 = static_cast<int>(K0 >> 3);
     const int nvec = nvec0 + static_cast<int>(K1 >> 3);
-    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * 4; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * 4) {
-        const int64_t row = row0 + row_in_cta;
-        const bool row_ok = row < M;
-        uint4 raw[VPT];
+    auto load_row = [&](int64_t row, uint4 (&dst)[VPT]) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int vec = i * kThreadsPerRow + t;
-            raw[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (row_ok && vec < nvec0)
-                raw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x0) + row * ld0 + static_cast<int64_t>(vec) * 8));
-            else if (row_ok && vec < nvec)
-                raw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x1) + row * ld1 + static_cast<int64_t>(vec - nvec0) * 8));
+            dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (row < M && vec < nvec0)
+                dst[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x0) + row * ld0 + static_cast<int64_t>(vec) * 8));
+            else if (row < M && vec < nvec)
+                dst[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(x1) + row * ld1 + static_cast<int64_t>(vec - nvec0) * 8));
         }
+    };
+    uint4 raw[VPT], next[VPT];
+    load_row(static_cast<int64_t>(blockIdx.x) * kRows + row_in_cta, raw);      // in flight while the table is copied
+    for (int i = threadIdx.x; i < 65536 / 8; i += kTableThreads)
+        reinterpret_cast<uint4*>(s_table)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+    __syncthreads();
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kRows;
+    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRows; row0 < M; row0 += stride) {
+        const int64_t row = row0 + row_in_cta;
+        const bool row_ok = row < M;
+        load_row(row + stride, next);          // the next row's loads fly under this row's look-ups and stores
         auto look2 = [&](uint32_t w) -> uint32_t {
             return static_cast<uint32_t>(s_table[w & 0xFFFFu]) | (static_cast<uint32_t>(s_table[w >> 16]) << 16);
         };
@@ -443,6 +495,8 @@ gelu_quant_table_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, co
         }
         const float amax = row_max(packed_absmax<DT, VPT>(raw), s_part, row_in_cta);
         quantise_and_store<DT, VPT>(raw, amax, row_ok, row, t, nvec, q, ldq, scale);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) raw[i] = next[i];
     }
 }
 
@@ -553,19 +607,14 @@ int i8f_quant_rowwise_ln_modulate(const void* x, int x_dtype, int64_t M, int64_t
     if (rc != I8F_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t nvec = K / 8;
-    static const int fast_ok = [] { const char* e = getenv("I8F_LN_FAST"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
-    if (fast_ok && nvec <= 4 * kThreadsPerRow) {
-        // rows of at most 4096 elements: persistent CTAs with the per-column constants in registers (same bits)
-        int sms = 148, dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int64_t want = (M + 1) / 2;
-        const unsigned grid_p = static_cast<unsigned>(want < 4LL * sms ? want : 4LL * sms);
+    if (nvec <= 512) {
+        // rows of at most 4096 elements: one warp per row
+        const unsigned grid_w = static_cast<unsigned>((M + kThreads / 32 - 1) / (kThreads / 32));
         if (x_dtype == I8F_BF16)
-            ln_modulate_quant_fast_kernel<I8F_BF16><<<grid_p, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
+            ln_modulate_quant_warp_kernel<I8F_BF16><<<grid_w, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
         else
-            ln_modulate_quant_fast_kernel<I8F_F16><<<grid_p, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
-        return check_launch("ln_modulate_quant_fast_kernel");
+            ln_modulate_quant_warp_kernel<I8F_F16><<<grid_w, kThreads, 0, st>>>(x, M, K, ldx, shift, scale, eps, q, ldq, row_scale, y_out, ldy);
+        return check_launch("ln_modulate_quant_warp_kernel");
     }
     const unsigned grid = static_cast<unsigned>((M + 1) / 2);
     if (x_dtype == I8F_BF16)
@@ -605,7 +654,7 @@ int i8f_quant_rowwise_gelu(const void* x_plain, int64_t K0, int64_t ld0, const v
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int64_t want = (M + 3) / 4;
+        const int64_t want = (M + 2) / 3;
         const unsigned grid = static_cast<unsigned>(want < sms ? want : sms);
         constexpr int kTableBytes = 65536 * 2;
 #define I8F_TABLE_GO(DT, V)                                                                                              \

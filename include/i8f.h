@@ -289,7 +289,8 @@ int i8f_lora_up_add(const void* t, int64_t ldt, const void* lora_b, int64_t ldb,
  *   w     = clamp(int32(w) + d8, -128, 127)
  * ws = w_scale[0] or w_scale[n] per w_scale_mode.  u comes from `uniforms`
  * (fp32 [N,K], pitch K) when non-NULL, else from Philox4x32-10 keyed by
- * `seed` with counter (n, k/4), word k%4, u = (word >> 8) * 2^-24.
+ * `seed` with counter (n, k/8): weight k takes 16-bit half (k%8)%2 (low half first) of word (k%8)/2,
+ * u = half * 2^-16 (one generator block serves eight weights).
  * factor_dtype is the dtype of up and down.
  * Replaces reconstruct_lora_diff (plain LoRA, int8_quant.py:139-155),
  * stochastic_round_int8_delta (:36-62) and the add/clamp at :313-316. */

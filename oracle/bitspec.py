@@ -321,69 +321,95 @@ def philox4x32_10(counter: np.ndarray, key: np.ndarray) -> np.ndarray:
 def philox_uniforms(seed: int, n_rows: int, n_cols: int) -> np.ndarray:
     """Uniforms in [0,1) for an [n_rows, n_cols] matrix.
 
-    Element (n, k) uses word k % 4 of Philox4x32-10 with
-    counter = (n, k // 4, 0, 0) and key = (seed low 32 bits, seed high 32 bits);
-    u = (word >> 8) * 2^-24, so u is exactly representable and below 1.
+    Element (n, k) uses Philox4x32-10 with counter = (n, k // 8, 0, 0) and key = (seed low 32 bits, seed high 32
+    bits): 16-bit half (k % 8) % 2 (low half first) of word (k % 8) // 2; u = half * 2^-16, so u is exactly
+    representable and below 1.  One generator block serves eight elements.
     """
-    groups = (n_cols + 3) // 4
+    groups = (n_cols + 7) // 8
     ctr = np.zeros((n_rows, groups, 4), dtype=np.uint32)
     ctr[..., 0] = np.arange(n_rows, dtype=np.uint32)[:, None]
     ctr[..., 1] = np.arange(groups, dtype=np.uint32)[None, :]
     key = np.zeros((n_rows, groups, 2), dtype=np.uint32)
     key[..., 0] = np.uint32(seed & 0xFFFFFFFF)
     key[..., 1] = np.uint32((seed >> 32) & 0xFFFFFFFF)
-    words = philox4x32_10(ctr, key).reshape(n_rows, groups * 4)[:, :n_cols]
-    return (words >> np.uint32(8)).astype(F32) * F32(2.0 ** -24)
+    words = philox4x32_10(ctr, key)                                    # [n_rows, groups, 4]
+    halves = np.stack([words & np.uint32(0xFFFF), words >> np.uint32(16)], axis=-1)   # [..., 4, 2]: low half first
+    halves = halves.reshape(n_rows, groups * 8)[:, :n_cols]
+    return halves.astype(F32) * F32(2.0 ** -16)
 
 
 # --------------------------------------------------------------------------
 # Quantiser prologues (no counterpart in the reference: the model's own element-wise steps in front of a
 # quantised linear, folded into the activation quantiser; defined by comfyui-int8-fast_b200/csrc/quant_prologue.cu)
 # --------------------------------------------------------------------------
-_ROW_THREADS = 128
+def rowsum_tree(v: np.ndarray, threads: int = 128) -> np.ndarray:
+    """Sum of every row of v [M, K] (K % 8 == 0) in the quantiser kernels' fixed order.
 
-
-def rowsum128(v: np.ndarray) -> np.ndarray:
-    """Sum of every row of v [M, K] (K % 8 == 0) in the quantiser's fixed order.
-
-    A row belongs to 128 threads; thread t holds the 8-element vectors t, t + 128, ...  Order of the fp32 additions:
-    the 8 elements of a vector left to right; a thread's vector sums in slot order; the 32 lanes of a warp as a
-    balanced binary tree (neighbours first); the four warps left to right.  Vectors past the end count as zeros.
+    A row belongs to `threads` threads (128: four warps; 32: one warp); thread t holds the 8-element vectors
+    t, t + threads, ...  Order of the fp32 additions: the 8 elements of a vector left to right; a thread's vector
+    sums in slot order; the 32 lanes of a warp as a balanced binary tree (neighbours first); the warps left to
+    right.  Vectors past the end count as zeros.
     """
     v = np.asarray(v, dtype=F32)
     M, K = v.shape
     nvec = K // 8
-    vpt = max(1, -(-nvec // _ROW_THREADS))
-    pad = np.zeros((M, vpt * _ROW_THREADS * 8), dtype=F32)
+    vpt = max(1, -(-nvec // threads))
+    pad = np.zeros((M, vpt * threads * 8), dtype=F32)
     pad[:, :K] = v
-    e = pad.reshape(M, vpt, _ROW_THREADS, 8)
+    e = pad.reshape(M, vpt, threads, 8)
     s = e[..., 0] + e[..., 1]
     for j in range(2, 8):
         s = s + e[..., j]
     t = s[:, 0, :]
     for i in range(1, vpt):
         t = t + s[:, i, :]
-    w = t.reshape(M, 4, 32)
+    w = t.reshape(M, threads // 32, 32)
     while w.shape[-1] > 1:
         w = w[..., 0::2] + w[..., 1::2]
     w = w[..., 0]
-    return ((w[:, 0] + w[:, 1]) + w[:, 2]) + w[:, 3]
+    total = w[:, 0]
+    for k in range(1, w.shape[1]):
+        total = total + w[:, k]
+    return total
+
+
+def rowsum128(v: np.ndarray) -> np.ndarray:
+    return rowsum_tree(v, 128)
+
+
+def round_f64_to(x: np.ndarray, dtype: str) -> np.ndarray:
+    """float64 values rounded ONCE (nearest even) to 'bf16' / 'f16', returned as fp32.  For values in the normal
+    range of the target type (what the tests produce); used where a kernel rounds an exact result directly to the
+    16-bit type (a fused multiply-add in that type) instead of through fp32."""
+    x = np.asarray(x, dtype=np.float64)
+    if dtype == "f16":
+        return x.astype(np.float16).astype(F32)
+    if dtype != "bf16":
+        raise ValueError(dtype)
+    bits = np.ascontiguousarray(x).view(np.uint64)
+    lsb = (bits >> np.uint64(45)) & np.uint64(1)
+    rounded = ((bits + np.uint64((1 << 44) - 1) + lsb) >> np.uint64(45)) << np.uint64(45)
+    out = rounded.view(np.float64)
+    out = np.where(np.isfinite(x), out, x)
+    return out.astype(F32)
 
 
 def layernorm_modulate(x: np.ndarray, shift: np.ndarray, scale: np.ndarray, eps: float = 1e-5, dtype: str = "bf16") -> np.ndarray:
     """y = rnd(rnd((x - mean) * rstd) * rnd(1 + scale) + shift): LayerNorm without affine parameters followed by the
-    adaptive modulation of a diffusion transformer block, every intermediate tensor in the activation dtype."""
+    adaptive modulation of a diffusion transformer block.  The row sums run in the order of `rowsum_tree`, with one
+    warp per row for rows of at most 4096 elements and 128 threads per row above; the last step is ONE rounding of the
+    exact value ln * gain + shift to the activation dtype (a fused multiply-add in that dtype)."""
     x = np.asarray(x, dtype=F32)
+    threads = 32 if x.shape[1] <= 4096 else 128
     K = F32(x.shape[1])
-    mean = (rowsum128(x) / K).astype(F32)[:, None]
+    mean = (rowsum_tree(x, threads) / K).astype(F32)[:, None]
     d = (x - mean).astype(F32)
-    var = (rowsum128(d * d) / K).astype(F32)[:, None]
+    var = (rowsum_tree(d * d, threads) / K).astype(F32)[:, None]
     rstd = (F32(1.0) / np.sqrt((var + F32(eps)).astype(F32))).astype(F32)
     ln = round_to(d * rstd, dtype)
-    one_plus = round_to(F32(1.0) + np.asarray(scale, dtype=F32).reshape(1, -1), dtype)
-    # ln * one_plus is exact in fp32 (two significands of at most 11 bits), so this is the single rounding of an FMA
-    prod = (ln.astype(np.float64) * one_plus.astype(np.float64))
-    return round_to((prod + np.asarray(shift, dtype=F32).reshape(1, -1).astype(np.float64)).astype(F32), dtype)
+    gain = round_to(F32(1.0) + np.asarray(scale, dtype=F32).reshape(1, -1), dtype)
+    exact = ln.astype(np.float64) * gain.astype(np.float64) + np.asarray(shift, dtype=F32).reshape(1, -1).astype(np.float64)
+    return round_f64_to(exact, dtype)
 
 
 _GELU_C0 = F32(0.7978845608028654)

@@ -488,6 +488,9 @@ def test_gelu_quantiser_bit_exact(cuda_pkg, M, K0, K1, dt):
     """[ plain | GELU_tanh ] -> per-token int8 in one kernel, the two parts read as column slices of wider matrices."""
     F, wl = cuda_pkg.functional, cuda_pkg.workloads
     wide = (wl.activation(M, K1 + 64, seed=51, dtype=torch.float32) * 1.5).to(dt).to(DEV)
+    if K1 >= 8:   # values on and beyond the edges of the look-up table of the large-input kernel, zeros of both signs
+        wide[0, 64:72] = torch.tensor([0.0, -0.0, 1e-5, -3e-6, 100.0, -100.0, 2.0 ** -12, 15.9375], dtype=dt, device=DEV)
+        wide[M - 1, 64:72] = torch.tensor([-(2.0 ** -12), 16.0, -16.0, 2.0 ** -13, -15.9375, 6e-8, 3e4, -3e4], dtype=dt, device=DEV)
     xg = wide[:, 64:]                                                 # a column slice, as in a fused qkv + mlp buffer
     xp = (wl.activation(M, K0, seed=52, dtype=torch.float32)).to(dt).to(DEV) if K0 else None
     q, rs, y = F.quantize_rowwise_gelu(xg, xp, return_y=True)
@@ -498,7 +501,7 @@ def test_gelu_quantiser_bit_exact(cuda_pkg, M, K0, K1, dt):
     got = y[:, K0:]
     d = (got.float() - lib.float()).abs()
     step = torch.exp2(torch.floor(torch.log2(lib.float().abs().clamp_min(2.0 ** -14))) - (7 if dt == torch.bfloat16 else 10))
-    assert bool((d <= step + 1e-6).all()) and (d > 0).float().mean().item() <= 0.01
+    assert bool((d <= step + 1e-6).all()) and (d > 0).float().mean().item() <= 0.01 + 16.0 / d.numel()   # 16 injected edge values
     # special values: zero, large magnitudes of both signs
     sp = torch.tensor([[0.0, -0.0, 30.0, -30.0, 1e4, -1e4, 1e-3, -1e-3]], dtype=dt, device=DEV)
     _, _, ysp = F.quantize_rowwise_gelu(sp, None, return_y=True)

@@ -174,6 +174,12 @@ def test_philox_known_answers():
     assert [int(v) for v in p] == [0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1]
     u = bs.philox_uniforms(318008, 7, 10)
     assert u.shape == (7, 10) and u.min() >= 0.0 and u.max() < 1.0
+    # mapping: element (n, k) <- counter (n, k // 8), word (k % 8) // 2, low half first, times 2^-16
+    blk = bs.philox4x32_10(np.array([[5, 1, 0, 0]], np.uint32), np.array([[318008, 0]], np.uint32))[0]
+    assert u[5, 8] == np.float32(int(blk[0]) & 0xFFFF) * np.float32(2.0 ** -16)
+    assert u[5, 9] == np.float32(int(blk[0]) >> 16) * np.float32(2.0 ** -16)
+    blk0 = bs.philox4x32_10(np.array([[5, 0, 0, 0]], np.uint32), np.array([[318008, 0]], np.uint32))[0]
+    assert u[5, 7] == np.float32(int(blk0[3]) >> 16) * np.float32(2.0 ** -16)
 
 
 @pytest.mark.parametrize("rows,cols", [(0, 128), (3, 0)])
