@@ -500,31 +500,52 @@ gelu_quant_table_kernel(const void* __restrict__ x0, int64_t K0, int64_t ld0, co
     }
 }
 
-// Device address of the table for `dt` on the current device, built on `st` the first time it is asked for.  While
-// `st` is being captured into a graph the build is captured with it (and not remembered, since it has not run yet).
+// Device address of the table for `dt` on the current device.  The first call on a device builds it with a kernel on
+// that call's stream and records an event behind it; until the event has completed, calls on other streams are made
+// to wait for it (stream-side, the host never blocks).  While `st` is being captured into a graph and the table is
+// not known to be complete, the build is captured with the launch instead (and not remembered: it has not run yet).
 int gelu_table(int dt, cudaStream_t st, const unsigned short** out) {
-    static unsigned short* base[64] = {nullptr};
-    static bool built[64][2] = {{false}};
+    struct State {
+        unsigned short* table;
+        cudaEvent_t built_event;
+        int phase;        // 0 nothing, 1 build enqueued (event recorded), 2 known complete
+    };
+    static State states[64][2] = {};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(I8F_ERR_CUDA, "cudaGetDevice failed");
-    if (base[dev] == nullptr) {
+    const int which = dt == I8F_BF16 ? 0 : 1;
+    State& s = states[dev][which];
+    if (s.table == nullptr) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_gelu_table);
         if (e != cudaSuccess || p == nullptr) return fail(I8F_ERR_CUDA, "cudaGetSymbolAddress(GELU table): %s", cudaGetErrorString(e));
-        base[dev] = static_cast<unsigned short*>(p);
+        s.table = static_cast<unsigned short*>(p) + which * 65536;
     }
-    const int which = dt == I8F_BF16 ? 0 : 1;
-    unsigned short* table = base[dev] + which * 65536;
-    if (!built[dev][which]) {
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(st, &cap);
-        if (which == 0) gelu_table_kernel<I8F_BF16><<<256, 256, 0, st>>>(table);
-        else gelu_table_kernel<I8F_F16><<<256, 256, 0, st>>>(table);
-        const int rc = check_launch("gelu_table_kernel");
-        if (rc != I8F_OK) return rc;
-        if (cap == cudaStreamCaptureStatusNone) built[dev][which] = true;
+    *out = s.table;
+    if (s.phase == 2) return I8F_OK;
+    if (s.phase == 1 && cudaEventQuery(s.built_event) == cudaSuccess) {
+        s.phase = 2;
+        return I8F_OK;
     }
-    *out = table;
+    auto build = [&]() -> int {
+        if (which == 0) gelu_table_kernel<I8F_BF16><<<256, 256, 0, st>>>(s.table);
+        else gelu_table_kernel<I8F_F16><<<256, 256, 0, st>>>(s.table);
+        return check_launch("gelu_table_kernel");
+    };
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cap);
+    if (cap != cudaStreamCaptureStatusNone) return build();       // part of the graph; rebuilding the same values is harmless
+    if (s.phase == 1) {
+        const cudaError_t e = cudaStreamWaitEvent(st, s.built_event, 0);
+        if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "cudaStreamWaitEvent(GELU table): %s", cudaGetErrorString(e));
+        return I8F_OK;
+    }
+    int rc = build();
+    if (rc != I8F_OK) return rc;
+    cudaError_t e = cudaEventCreateWithFlags(&s.built_event, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(s.built_event, st);
+    if (e != cudaSuccess) return fail(I8F_ERR_CUDA, "recording the GELU table event: %s", cudaGetErrorString(e));
+    s.phase = 1;
     return I8F_OK;
 }
 
