@@ -295,16 +295,23 @@ def parity_record(pkg, shape, s, dev):
            "int32_accumulators_equal": bool(torch.equal(acc.cpu(), acc_want))}
     del acc
     yc = y.cpu()
+    base = want
     if s["lora"] is not None:
         want = tp.lora_dynamic_add(want, xr, s["lora"][0].cpu(), s["lora"][1].cpu())
         yc = pkg.custom_ops.linear_lora_forward(s["x"], s["wq"], s["ws"], s["bias"], s["lora"][0], s["lora"][1], torch.bfloat16,
                                                 shape.hadamard, False, 0).cpu()
     rms = float(want.double().pow(2).mean().sqrt())
+    d = (yc.float() - want.float()).abs()
     rec["out_bits_equal"] = bool(torch.equal(yc.view(torch.int16), want.view(torch.int16)))
-    rec["out_max_abs_err_over_rms"] = float((yc.double() - want.double()).abs().max()) / rms
+    rec["out_max_abs_err_over_rms"] = float(d.max()) / rms
     rec["out_tolerance"] = 1e-2
+    # where bf16 itself is coarser than 1e-2 RMS (outputs of several RMS in magnitude), two bf16 steps at the magnitude of
+    # the terms is the bar instead; only the dynamic-LoRA path (tensor-core float sums) ever needs it
+    mag = torch.maximum(torch.maximum(base.float().abs(), (want.float() - base.float()).abs()), want.float().abs())
+    step = torch.exp2(torch.floor(torch.log2(mag.clamp_min(2.0 ** -126))) - 7)
+    rec["out_elements_outside_bar"] = int((~((d <= 1e-2 * rms) | (d <= 2 * step))).sum())
     rec["ok"] = bool(rec["int8_activations_equal"] and rec["activation_scales_equal"] and rec["int32_accumulators_equal"]
-                     and rec["out_max_abs_err_over_rms"] <= 1e-2)
+                     and rec["out_elements_outside_bar"] == 0)
     rec["seconds"] = round(time.perf_counter() - t0, 2)
     return rec
 

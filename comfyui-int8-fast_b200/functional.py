@@ -36,6 +36,16 @@ def _code(dtype: torch.dtype) -> int:
         raise TypeError(f"unsupported dtype {dtype}; expected bf16, fp16 or fp32") from None
 
 
+_WORKSPACE_BYTES: dict = {}
+
+
+def _workspace_need(M: int, K: int) -> int:
+    need = _WORKSPACE_BYTES.get((M, K))
+    if need is None:
+        need = _WORKSPACE_BYTES[(M, K)] = int(nat.load().i8f_linear_workspace_bytes(M, K))
+    return need
+
+
 def _wscale_arg(w_scale, device: torch.device, n_rows: int) -> tuple[Tensor, int]:
     """Device fp32 tensor + granularity code from a float, 0-d/1-element tensor or [N,1]/[N] tensor.
 
@@ -45,12 +55,14 @@ def _wscale_arg(w_scale, device: torch.device, n_rows: int) -> tuple[Tensor, int
     """
     if not isinstance(w_scale, Tensor):
         return torch.tensor([float(w_scale)], dtype=torch.float32, device=device), nat.WSCALE_TENSOR
-    ws = w_scale.to(device=device, dtype=torch.float32)
+    ws = w_scale
+    if ws.dtype is not torch.float32 or ws.device != device:
+        ws = ws.to(device=device, dtype=torch.float32)
     if ws.numel() == 1:
-        return ws.reshape(1), nat.WSCALE_TENSOR
+        return ws, nat.WSCALE_TENSOR        # one element: the pointer is all the library needs, whatever the shape
     if ws.numel() != n_rows:
         raise ValueError(f"weight scale has {ws.numel()} entries; expected 1 or one per weight row ({n_rows})")
-    return ws.reshape(-1).contiguous(), nat.WSCALE_CHANNEL
+    return (ws if ws.is_contiguous() else ws.contiguous()), nat.WSCALE_CHANNEL   # [N] and [N,1] share their memory layout
 
 
 def _check_weight(w: Tensor, K: int) -> None:
@@ -282,25 +294,28 @@ def linear_w8a8_scatter(q: Tensor, q_scale: Tensor, w: Tensor, w_scale, bias: Te
 def linear_forward(x: Tensor, w: Tensor, w_scale, bias: Tensor | None, out_dtype: torch.dtype, hadamard: bool = False,
                    order: int = nat.EPI_PYTORCH, workspace: Tensor | None = None) -> Tensor:
     """(rotate) -> quantise -> int8 GEMM -> dequant (+bias) through the single fused entry point."""
-    nat.require_device(x.device)
+    device = x.device
+    nat.require_device(device)
     x, w = _rows(x), _rows(w)
     M, K = x.shape
     N = w.shape[0]
     _check_weight(w, K)
-    ws, mode = _wscale_arg(w_scale, x.device, N)
-    if bias is not None:
-        bias = bias.to(x.device).contiguous()
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    ws, mode = _wscale_arg(w_scale, device, N)
+    if bias is not None and (bias.device != device or not bias.is_contiguous()):
+        bias = bias.to(device).contiguous()
+    out = torch.empty((M, N), dtype=out_dtype, device=device)
     if M == 0 or N == 0:
         return out
-    need = nat.load().i8f_linear_workspace_bytes(M, K)
+    need = _workspace_need(M, K)
     if workspace is None or workspace.numel() * workspace.element_size() < need:
-        workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
-    nat.check(nat.load().i8f_linear_forward(nat.ptr(x), _code(x.dtype), _ld(x), 1 if hadamard else 0, nat.ptr(w), _ld(w),
-                                            nat.ptr(ws), mode, nat.ptr(bias), _code(bias.dtype) if bias is not None else 0,
-                                            nat.ptr(out), _code(out_dtype), N, M, N, K, order, nat.ptr(workspace),
-                                            workspace.numel() * workspace.element_size(), nat.current_stream(x.device)),
-              "i8f_linear_forward")
+        workspace = torch.empty((need,), dtype=torch.uint8, device=device)
+    rc = nat.load().i8f_linear_forward(x.data_ptr(), _code(x.dtype), _ld(x), 1 if hadamard else 0, w.data_ptr(), _ld(w),
+                                       ws.data_ptr(), mode, bias.data_ptr() if bias is not None else None,
+                                       _code(bias.dtype) if bias is not None else 0, out.data_ptr(), _code(out_dtype), N, M, N, K,
+                                       order, workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                       nat.current_stream(device))
+    if rc:
+        nat.check(rc, "i8f_linear_forward")
     return out
 
 

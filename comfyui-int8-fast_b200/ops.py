@@ -560,8 +560,11 @@ def _define_ops(manual_cast, cast_bias_weight, uncast_bias_weight):
                                                        self._use_quarot, Int8TensorwiseOps.lora_uses_rotated_input,
                                                        nat.EPI_PYTORCH)
                 elif rows > SMALL_BATCH_ROWS:
-                    y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
-                                                  nat.EPI_PYTORCH)
+                    if torch.compiler.is_compiling():    # one opaque node for the tracer
+                        y = custom_ops.linear_forward(x2, weight, w_scale, bias, compute_dtype, self._use_quarot,
+                                                      nat.EPI_PYTORCH)
+                    else:                                # eager: straight to the library, without the operator dispatch
+                        y = F.linear_forward(x2, weight, w_scale, bias, compute_dtype, hadamard=self._use_quarot)
                 else:
                     lora_a, lora_b = _prepare_lora(self, x.device, compute_dtype) if has_lora else (None, None)
                     y = custom_ops.small_batch_forward(x2, weight, w_scale, bias, lora_a, lora_b, self._use_quarot)

@@ -109,7 +109,10 @@ int i8f_quant_rowwise_ln_modulate(const void* x, int x_dtype, int64_t M, int64_t
 
 /* y = [ x_plain [M,K0] | rnd(GELU_tanh(x_gelu [M,K1])) ] row by row (either part may be empty), then q [M,K0+K1],
  * row_scale as i8f_quant_rowwise computes them from y.  The GELU is x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715
- * x^3), evaluated in correctly rounded fp32 operations only.  y_out (may be NULL) receives y. */
+ * x^3), evaluated in correctly rounded fp32 operations only.  y_out (may be NULL) receives y.  Large inputs read
+ * rnd(GELU(x)) from a table of all 65536 16-bit values (same bits): 256 KB inside the library image, filled by a
+ * kernel on this call's stream the first time a device needs it; calls on other streams are ordered behind that
+ * build with an event, nothing is allocated and the host never waits. */
 int i8f_quant_rowwise_gelu(const void* x_plain, int64_t K0, int64_t ld0, const void* x_gelu, int64_t K1, int64_t ld1,
                            int x_dtype, int64_t M, int8_t* q, int64_t ldq, float* row_scale,
                            void* y_out, int64_t ldy, void* stream);

@@ -353,7 +353,7 @@ def test_weight_scale_length_is_checked_on_the_host(pkg):
     F = pkg.functional
     cpu = torch.device("cpu")
     ws, mode = F._wscale_arg(torch.ones(7, 1), cpu, 7)
-    assert mode == pkg._native.WSCALE_CHANNEL and ws.shape == (7,)
+    assert mode == pkg._native.WSCALE_CHANNEL and ws.numel() == 7 and ws.is_contiguous()
     assert F._wscale_arg(0.5, cpu, 7)[1] == pkg._native.WSCALE_TENSOR
     assert F._wscale_arg(torch.tensor(0.5), cpu, 7)[1] == pkg._native.WSCALE_TENSOR
     for bad in (torch.ones(6), torch.ones(7, 2), torch.ones(14)):
