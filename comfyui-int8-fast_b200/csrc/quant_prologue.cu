@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "f32x2.cuh"
 #include "host_common.h"
 
 namespace i8f {
@@ -83,14 +84,28 @@ __device__ __forceinline__ float round_to_dt(float x) {
     else return __half2float(__float2half_rn(x));
 }
 
-// rint(x * inv) for four values, packed as int8 (see quant_rowwise.cu: |x * inv| <= 127.00002)
-__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv) {
+// rint(x * inv) for the eight values of a vector: the product is rounded first (scalar __fmul_rn, which the assembler
+// never contracts with the add that follows; a two-wide multiply was seen contracted), then the magic add runs
+// two-wide.  |x * inv| <= 127.00002, see quant_rowwise.cu.
+__device__ __forceinline__ uint2 quant8_pairs(const float (&f)[8], float inv) {
     constexpr float kMagic = 12582912.0f;
-    const uint32_t ua = __float_as_uint(__fadd_rn(__fmul_rn(a, inv), kMagic));
-    const uint32_t ub = __float_as_uint(__fadd_rn(__fmul_rn(b, inv), kMagic));
-    const uint32_t uc = __float_as_uint(__fadd_rn(__fmul_rn(c, inv), kMagic));
-    const uint32_t ud = __float_as_uint(__fadd_rn(__fmul_rn(d, inv), kMagic));
-    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
+    const f32x2 magic2 = pair_of(kMagic, kMagic);
+    uint32_t u[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        halves_bits(add2(pair_of(__fmul_rn(f[2 * j], inv), __fmul_rn(f[2 * j + 1], inv)), magic2), u[2 * j], u[2 * j + 1]);
+    uint2 o;
+    o.x = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+    o.y = __byte_perm(__byte_perm(u[4], u[5], 0x0040), __byte_perm(u[6], u[7], 0x0040), 0x5410);
+    return o;
+}
+
+// seq_sum8 of two vectors at once, one in each lane of the two-wide registers (same order of additions per vector).
+__device__ __forceinline__ void seq_sum8_two(const float (&a)[8], const float (&b)[8], float& sa, float& sb) {
+    f32x2 s = add2(pair_of(a[0], b[0]), pair_of(a[1], b[1]));
+#pragma unroll
+    for (int j = 2; j < 8; ++j) s = add2(s, pair_of(a[j], b[j]));
+    halves(s, sa, sb);
 }
 
 // Sum over the 128 threads of a row of one value per thread, in the fixed order of the header.  `s_part` has one
@@ -156,10 +171,7 @@ __device__ __forceinline__ void quantise_and_store(const uint4 (&raw)[VPT], floa
         if (row_ok && vec < nvec) {
             float f[8];
             unpack8<DT>(raw[i], f);
-            uint2 o;
-            o.x = quant4(f[0], f[1], f[2], f[3], inv);
-            o.y = quant4(f[4], f[5], f[6], f[7], inv);
-            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = o;
+            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = quant8_pairs(f, inv);
         }
     }
 }
@@ -280,31 +292,46 @@ ln_modulate_quant_warp_kernel(const void* __restrict__ x, int64_t M, int64_t K, 
         for (int d = 1; d < 32; d <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
         return v;
     };
+    // the two sum passes take the lane's vectors two at a time, one vector in each lane of the two-wide registers
     float part = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        float f[8];
-        unpack8_again<DT>(raw[i], f);
-        const float sv = seq_sum8(f);
-        part = (i == 0) ? sv : __fadd_rn(part, sv);
+    for (int i = 0; i < VPL; i += 2) {
+        float fa[8], fb[8], sa, sb;
+        unpack8_again<DT>(raw[i], fa);
+        unpack8_again<DT>(raw[i + 1], fb);
+        seq_sum8_two(fa, fb, sa, sb);
+        part = (i == 0) ? sa : __fadd_rn(part, sa);
+        part = __fadd_rn(part, sb);
     }
     const float mean = __fdiv_rn(warp_sum(part), kf);
+    const f32x2 mean2 = pair_of(mean, mean);
     part = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        const int vec = i * 32 + lane;
-        float f[8];
-        unpack8_again<DT>(raw[i], f);
+    for (int i = 0; i < VPL; i += 2) {
+        const bool oka = i * 32 + lane < nvec, okb = (i + 1) * 32 + lane < nvec;
+        float fa[8], fb[8];
+        unpack8_again<DT>(raw[i], fa);
+        unpack8_again<DT>(raw[i + 1], fb);
+        f32x2 sq[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float d = (vec < nvec) ? __fsub_rn(f[j], mean) : 0.f;
-            f[j] = __fmul_rn(d, d);
+            float da, db;
+            halves(sub2(pair_of(fa[j], fb[j]), mean2), da, db);
+            sq[j] = pair_of(__fmul_rn(da, da), __fmul_rn(db, db));   // scalar: never contracted with the sums below
         }
-        const float sv = seq_sum8(f);
-        part = (i == 0) ? sv : __fadd_rn(part, sv);
+        f32x2 s2 = add2(sq[0], sq[1]);
+#pragma unroll
+        for (int j = 2; j < 8; ++j) s2 = add2(s2, sq[j]);
+        float sa, sb;
+        halves(s2, sa, sb);
+        sa = oka ? sa : 0.f;      // vectors beyond the row contribute zeros
+        sb = okb ? sb : 0.f;
+        part = (i == 0) ? sa : __fadd_rn(part, sa);
+        part = __fadd_rn(part, sb);
     }
     const float var = __fdiv_rn(warp_sum(part), kf);
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+    const f32x2 rstd2 = pair_of(rstd, rstd);
     uint32_t m2 = 0u;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -318,7 +345,9 @@ ln_modulate_quant_warp_kernel(const void* __restrict__ x, int64_t M, int64_t K, 
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t ln2 = pack2<DT>(__fmul_rn(__fsub_rn(f[2 * j], mean), rstd), __fmul_rn(__fsub_rn(f[2 * j + 1], mean), rstd));
+                float lnlo, lnhi;
+                halves(mul2(sub2(pair_of(f[2 * j], f[2 * j + 1]), mean2), rstd2), lnlo, lnhi);
+                const uint32_t ln2 = pack2<DT>(lnlo, lnhi);
                 if constexpr (DT == I8F_BF16) {
                     const __nv_bfloat162 one = __floats2bfloat162_rn(1.0f, 1.0f);
                     const __nv_bfloat162 gain = __hadd2(one, *reinterpret_cast<const __nv_bfloat162*>(&msw[j]));
@@ -354,10 +383,7 @@ ln_modulate_quant_warp_kernel(const void* __restrict__ x, int64_t M, int64_t K, 
         if (vec < nvec) {
             float f[8];
             unpack8_again<DT>(raw[i], f);
-            uint2 o;
-            o.x = quant4(f[0], f[1], f[2], f[3], inv);
-            o.y = quant4(f[4], f[5], f[6], f[7], inv);
-            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = o;
+            *reinterpret_cast<uint2*>(q + row * ldq + static_cast<int64_t>(vec) * 8) = quant8_pairs(f, inv);
         }
     }
 }
