@@ -60,6 +60,28 @@ def test_quant_rowwise_bit_exact(cuda_pkg, M, K, had, dt):
         assert np.array_equal(to_np(xrot), xr)
 
 
+@pytest.mark.parametrize("M,K,dt", [
+    (2051, 4096, torch.bfloat16), (2048, 8192, torch.float16), (4099, 4096, torch.float16), (2300, 8192, torch.bfloat16),
+])
+def test_quant_rowwise_rotated_many_rows_bit_exact(cuda_pkg, M, K, dt):
+    """Rotated rows of 4096 / 8192 elements, thousands of rows (several waves of CTAs), row counts that are no multiple
+    of the rows per CTA, a pitched input."""
+    F, wl = cuda_pkg.functional, cuda_pkg.workloads
+    x = wl.activation(M, K, seed=11, dtype=dt)
+    xr = bs.rotate_activation(to_np(x), NAME[dt])
+    q_want, s_want = bs.quantize_rowwise(xr)
+    q, s = F.quantize_rowwise(x.to(DEV), hadamard=True)
+    assert np.array_equal(to_np(q), q_want)
+    assert np.array_equal(to_np(s), s_want)
+    wide = torch.zeros(M, K + 64, dtype=dt, device=DEV)
+    wide[:, 32:32 + K] = x.to(DEV)
+    q2, s2 = F.quantize_rowwise(wide[:, 32:32 + K], hadamard=True)
+    assert torch.equal(q2, q) and torch.equal(s2, s)
+    # asking for the rotated copy as well changes nothing
+    q3, s3, _ = F.quantize_rowwise(x.to(DEV), hadamard=True, return_rotated=True)
+    assert torch.equal(q3, q) and torch.equal(s3, s)
+
+
 def test_quant_edge_rows(cuda_pkg):
     """All-zero rows take the 1e-30 floor; a strided (pitched) input is read in place."""
     F = cuda_pkg.functional
