@@ -73,6 +73,7 @@ struct GemmParams {
     int wide_out;       // scatter mode: 64-column (128-byte) store boxes
     int n_out;   // number of destinations (tensor maps) every output chunk is stored to
     int out_col0; // column of the destination matrices at which this launch's block starts
+    int k_split;  // 1, or 2: the two CTAs of a cluster each take half of K for the same tile (single-CTA kernels)
     int* status;
 };
 
@@ -422,8 +423,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-    const int tile_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    // K split (single-CTA kernels, sub-wave problems): a cluster of two CTAs owns ONE tile, each CTA runs half of the K
+    // slabs into its own tensor memory, the second CTA hands its partial tile to the first through distributed shared
+    // memory and the first one runs the epilogue.  The tensor core takes one row of A per cycle whatever the tile's
+    // width, so a narrow problem gets faster only by putting more SMs on its rows x K.
+    const bool ksplit = !PAIR && p.k_split == 2;
+    const uint32_t krank = ksplit ? cluster_ctarank() : 0u;
+    const int tile_step = (PAIR || ksplit) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int tile_first = (PAIR || ksplit) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int kb_begin = ksplit ? static_cast<int>(krank) * (p.num_k_blocks >> 1) : 0;
+    const int kb_end = (ksplit && krank == 0) ? (p.num_k_blocks >> 1) : p.num_k_blocks;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -435,7 +444,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 tile_coords(t, p.tiles_m, p.tiles_n, m_blk, n_blk);
                 const int row_a = m_blk * C::kTileM + static_cast<int>(rank) * kBM;
                 const int row_b = n_blk * BN + static_cast<int>(rank) * C::kBRows;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, p.status, kStEmptyWait)) {
                         ok = false;
                         break;
@@ -478,6 +487,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
             }
         }
+        if (ksplit) {   // every thread of both CTAs takes part in the two barriers of the hand-over (see the epilogue)
+            cluster_arrive();
+            cluster_wait();
+            cluster_arrive();
+            cluster_wait();
+        }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             int stage = 0;
@@ -485,16 +500,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int buf = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            // `ready`: the full barrier of the slab about to be consumed was already seen complete.  Each iteration
+            // asks for the NEXT slab's barrier before it issues its own MMAs, so the round trip of that query passes
+            // under the MMA issue instead of in front of it (the issue loop, not the tensor core, bounds narrow tiles).
+            bool ready = false;
             for (int t = tile_first; ok && t < num_tiles; t += tile_step) {
                 if (!mbar_wait_bounded(accempty0 + 8 * buf, acc_phase ^ 1u, abort_flag, p.status, kStAccEmptyWait)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
+                for (int kb = 0; kb < kb_end - kb_begin; ++kb) {
+                    if (!ready && !mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
+                    {
+                        const int next_stage = stage + 1 == C::kStages ? 0 : stage + 1;
+                        const uint32_t next_phase = stage + 1 == C::kStages ? phase ^ 1u : phase;
+                        ready = mbar_try_wait(full0 + 8 * next_stage, next_phase);
+                    }
                     const uint32_t a_src = smem_base + stage * C::kStageBytes;
                     const uint64_t adesc = make_smem_desc_sw128(a_src);
                     const uint64_t bdesc = make_smem_desc_sw128(a_src + C::kABytes);
@@ -530,10 +554,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         tc_fence_after_sync();
                     }
                     for (int lb = 0; lb < p.lora_k_blocks; ++lb) {
-                        if (!mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
+                        if (!ready && !mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, p.status, kStFullWait)) {
                             ok = false;
                             break;
                         }
+                        ready = false;
                         tc_fence_after_sync();
                         const uint32_t a_src = smem_base + stage * C::kStageBytes;
                         const uint64_t adesc = make_smem_desc_sw128(a_src);
@@ -554,6 +579,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if constexpr (C::kAccBufs == 2) buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }
+        }
+        if (ksplit) {
+            cluster_arrive();
+            cluster_wait();
+            cluster_arrive();
+            cluster_wait();
         }
     } else {
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
@@ -621,9 +652,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             old_next.valid = false;
             if (need_old && c_first < c_end)   // in flight while the MMAs finish
                 prefetch_old(p, row, row_ok, n_blk * BN + c_first * 32, old_next);
-            if (!mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait)) break;
+            const bool acc_ok = mbar_wait_bounded(accfull0 + 8 * buf, acc_phase, abort_flag, p.status, kStAccFullWait);
+            if (!acc_ok && !ksplit) break;
             tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+            if constexpr (!PAIR) {
+                if (ksplit) {
+                    // Both CTAs' MMAs are complete once both have passed this barrier: the first CTA's operand ring is
+                    // then free and serves as the landing zone, [chunk][word of the row's 32][row of the tile]: a warp's
+                    // remote store and the first CTA's later load both cover 128 contiguous bytes.
+                    cluster_arrive();
+                    cluster_wait();
+                    if (krank == 1 && acc_ok) {
+                        const int row_in_tile = quarter * 32 + lane;
+                        for (int c = c_first; c < c_end; ++c) {
+                            uint32_t v[32];
+                            tmem_ld_32x32(t_addr + c * 32, v);
+                            tmem_ld_wait();
+                            // word j of row r at [chunk][j][r]: a warp's store covers 128 contiguous bytes
+                            const uint32_t dst0 = mapa_cluster(smem_base + static_cast<uint32_t>(c * kBM * 128 + row_in_tile * 4), 0);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(dst0 + static_cast<uint32_t>(j * kBM * 4)), "r"(v[j])
+                                             : "memory");
+                        }
+                    }
+                    cluster_arrive();      // release: the partial tile is written ...
+                    cluster_wait();        // ... acquire: and visible to the first CTA
+                    if (krank == 1 || !acc_ok) break;
+                }
+            }
             const uint32_t t_lora = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(C::kLoraCol);
             bool released = false;
 #pragma unroll 1
@@ -652,6 +710,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     __syncwarp();
                 }
                 tmem_ld_wait();
+                if constexpr (!PAIR) {
+                    if (ksplit) {   // + the second CTA's half of K: exact for int32, one more fp32 add for the 16-bit kinds
+                        const int row_in_tile = quarter * 32 + lane;
+                        const uint32_t* col0 = reinterpret_cast<const uint32_t*>(gen_base + c * kBM * 128) + row_in_tile;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t part = col0[j * kBM];
+                            if constexpr (KIND == kKindI8) v[j] += part;
+                            else v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(part)));
+                        }
+                    }
+                }
                 if (C::kAccBufs == 1 && c == c_end - 1) {
                     // single accumulator buffer (the next tile's MMAs wait for this): the last values of this warp's
                     // share are in registers, hand the accumulator back before the arithmetic and the store of this
@@ -878,7 +948,7 @@ struct LoraOperands {
 
 template <int KIND, int BN, bool PAIR, bool LORA = false>
 int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K, GemmParams p,
-                cudaStream_t st, const Scatter* scatter = nullptr, const LoraOperands* lo = nullptr) {
+                cudaStream_t st, const Scatter* scatter = nullptr, const LoraOperands* lo = nullptr, int k_split = 1) {
     using C = Cfg<BN, PAIR, LORA>;
     CUtensorMap tmA, tmB;
     LoraMaps lmaps{};
@@ -923,6 +993,7 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
     p.M = static_cast<int>(M);
     p.N = static_cast<int>(N);
     p.num_k_blocks = static_cast<int>((K + k_per_stage - 1) / k_per_stage);
+    p.k_split = (!PAIR && k_split == 2) ? 2 : 1;
     p.tiles_m = static_cast<int>((M + C::kTileM - 1) / C::kTileM);
     p.tiles_n = static_cast<int>((N + BN - 1) / BN);
     p.status = device_status_word();
@@ -962,12 +1033,21 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
         const char* e = getenv("I8F_PDL");
         return (e != nullptr && e[0] == '0') ? 0 : 1;
     }();
-    cudaLaunchAttribute at[2]{};
+    cudaLaunchAttribute at[3]{};
     int n_at = 0;
     if (PAIR) {
         I8F_REQUIRE(max_clusters[dev] > 0, I8F_ERR_CUDA, "no CTA pair fits on this device");
         const long long clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
         cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+        at[n_at].id = cudaLaunchAttributeClusterDimension;
+        at[n_at].val.clusterDim.x = 2;
+        at[n_at].val.clusterDim.y = 1;
+        at[n_at].val.clusterDim.z = 1;
+        ++n_at;
+    } else if (p.k_split == 2) {
+        // one tile per cluster of two CTAs (the caller checked that they fit one wave and that K has two halves)
+        I8F_REQUIRE(2 * tiles <= sm_count() && p.num_k_blocks >= 2, I8F_ERR_INVALID_ARG, "K split needs 2 * tiles <= SMs");
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * tiles), 1, 1);
         at[n_at].id = cudaLaunchAttributeClusterDimension;
         at[n_at].val.clusterDim.x = 2;
         at[n_at].val.clusterDim.y = 1;
@@ -1009,6 +1089,7 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
         const char* f = getenv("I8F_GEMM_SINGLE_CTA");
         return (f != nullptr && f[0] == '1') ? 5 : 0;
     }();
+    int k_split = 1;
     int choice;   // 1 pair 256 x 256, 2 single 128 x 256, 3 single 128 x 128, 4 single 128 x 64, 5 single 128 x 32
     if ((forced >= 1 && forced <= 4) || forced == 6) {
         choice = forced == 6 ? 5 : forced;
@@ -1032,13 +1113,51 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
             if (choice == 0 || ctas[c] > ctas[choice] || (ctas[c] == ctas[choice] && work[c] < work[choice])) choice = c;
         }
         if (choice == 0) choice = N > 128 ? ((M > 128 && forced != 5) ? 1 : 2) : (N > 64 ? 3 : 4);
+        // K split: when a single-CTA configuration leaves at least half of the SMs without a tile, two CTAs may share
+        // each tile's K range.  Estimated cycles of one CTA, fitted to measurements on M = 17 .. 512, K = 3072 .. 12288:
+        // K slabs x max(560 issue-and-tensor cycles, operand bytes at 72 B/clk), 1100 per 32-column chunk of the epilogue,
+        // 3700 + 950 per chunk for the hand-over.  The split is taken when its best candidate is at least 7 % cheaper than
+        // the best unsplit one (I8F_KSPLIT=0 switches it off).
+        static const int ksplit_on = [] {
+            const char* e = getenv("I8F_KSPLIT");
+            return (e != nullptr && e[0] == '0') ? 0 : 1;
+        }();
+        if (ksplit_on && scatter == nullptr && forced == 0) {
+            const int esz = KIND == kKindI8 ? 1 : 2;
+            const int64_t nkb = (K * esz + kStageRowBytes - 1) / kStageRowBytes;
+            const int bn_of[6] = {0, 256, 256, 128, 64, 32};
+            auto est = [&](int c, int split) -> int64_t {
+                const int64_t chunks = bn_of[c] / 32;
+                const int64_t slab_bytes = (c == 1 ? 16384 + 128 * 128 : 16384 + bn_of[c] * 128);
+                const int64_t slab = slab_bytes / 72 > 560 ? slab_bytes / 72 : 560;
+                return (nkb / split) * slab + chunks * 1100 + (split == 2 ? 3700 + chunks * 950 : 0);
+            };
+            int64_t best[3] = {0, -1, -1};
+            int best_c = 0;
+            for (int c = 1; c <= 5; ++c) {
+                if (ctas[c] > sms) continue;
+                for (int split = 1; split <= 2; ++split) {
+                    if (split == 2 && (c == 1 || 2 * ctas[c] > sms || nkb < 8)) continue;
+                    const int64_t e = est(c, split);
+                    if (best[split] < 0 || e < best[split]) {
+                        best[split] = e;
+                        if (split == 2) best_c = c;
+                    }
+                }
+            }
+            const int best_split = (best[2] >= 0 && best[1] >= 0 && best[2] * 100 < best[1] * 93) ? 2 : 1;
+            if (best_c != 0 && best_split == 2) {
+                choice = best_c;
+                k_split = 2;
+            }
+        }
     }
     switch (choice) {
         case 1: return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st, scatter);
-        case 2: return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
-        case 3: return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
-        case 5: return launch_gemm<KIND, 32, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
-        default: return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st, scatter);
+        case 2: return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
+        case 3: return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
+        case 5: return launch_gemm<KIND, 32, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
+        default: return launch_gemm<KIND, 64, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
     }
 }
 

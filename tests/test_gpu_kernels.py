@@ -127,6 +127,8 @@ def test_weight_quant_bit_exact(cuda_pkg, N, K, had, dt):
 @pytest.mark.parametrize("M,N,K", [
     (128, 256, 128), (128, 256, 4096), (256, 512, 1024), (1024, 2048, 512), (200, 328, 528), (17, 40, 16),
     (1, 8, 64), (129, 100, 144), (300, 64, 272), (16, 16, 16), (4608, 300, 192), (2048, 12288, 256),
+    # few tiles and a long K: two CTAs of a cluster share each tile's K range (an odd number of K slabs included)
+    (64, 4096, 4096), (17, 4104, 4224), (512, 4096, 12288), (130, 520, 8192),
 ])
 def test_gemm_int32_bit_exact(cuda_pkg, M, N, K):
     gen = torch.Generator().manual_seed(M * 7 + N * 3 + K)
@@ -171,6 +173,7 @@ def test_gemm_linearity_at_full_size(cuda_pkg):
     (130, 256, 520, False, True, True, 1, torch.bfloat16),
     (130, 256, 520, True, True, False, 1, torch.bfloat16),
     (64, 384, 200, True, True, False, 0, torch.float16),
+    (64, 4096, 1000, True, True, True, 0, torch.bfloat16), (40, 8192, 520, False, True, False, 1, torch.float16),
     (17, 128, 72, False, False, False, 0, torch.float16),
     (90, 640, 77, True, True, False, 0, torch.bfloat16),     # N not a multiple of 8: scalar store path
 ])
