@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the W8A8 linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2|c2merge|c4|dit|smallm] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2|c2merge|c4|dit|smallm|prologue|subwave]
+                    [--impl reference]
 
 One "step" is one pass of the hot path over one batch of synthetic input:
 (Hadamard rotation +) per-token int8 quantisation, the int8 tensor-core GEMM
@@ -1308,12 +1309,98 @@ def run_prologue(args):
                       "kernels": out, "gpu_launches": 8 * len(cases), "device_status": pkg._native.device_status()}))
 
 
+def run_subwave(args):
+    """GEMMs that do not fill one wave of tiles (few tokens, the text stream of the DiT, the LoRA down projection): one
+    JSON line with the CUDA-graph-timed launch of each, cuBLAS `torch._int_mm` on the same int8 operands beside the
+    int8 ones (no epilogue there), and an equality check of the int32 accumulators against it."""
+    import torch
+    import __graft_entry__ as g
+    rank, world, local_rank, dev, dist = rank_context()
+    pkg = g.load_package()
+    F = pkg.functional
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+
+    def timed(fn, n=20, reps=6):
+        side = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(n):
+                    fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / n)
+        del graph
+        return median(ts[1:])
+
+    out = {}
+    launches = 0
+    all_equal = True
+    for (M, K, N) in [(17, 4096, 4096), (64, 4096, 4096), (256, 3072, 3072), (512, 4096, 4096), (512, 4096, 12288),
+                      (512, 12288, 4096), (1024, 4096, 4096)]:
+        q = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8, device=dev)
+        w = torch.randint(-127, 128, (N, K), generator=gen, dtype=torch.int8, device=dev)
+        qs = torch.rand(M, 1, generator=gen, device=dev) * 0.02 + 0.001
+        ws = torch.full((1,), 0.01, device=dev)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: F.linear_w8a8(q, qs, w, ws, None, torch.bfloat16, out=y))
+        rec = {"ms": ms, "tops": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+        if M > 16:       # the library routine wants more than 16 rows
+            wt = w.t()
+            rec["int_mm_ms"] = timed(lambda: torch._int_mm(q, wt))
+            equal = bool(torch.equal(F.gemm_i8_i32(q, w), torch._int_mm(q, wt)))
+            rec["int32_equals_int_mm"] = equal
+            all_equal = all_equal and equal
+        out[f"w8a8 M={M} K={K} N={N}"] = rec
+        launches += 20
+    for (M, K, r) in [(8192, 4096, 64), (4608, 4096, 16)]:
+        x = torch.randn(M, K, generator=gen, device=dev).bfloat16()
+        a = (torch.randn(r, K, generator=gen, device=dev) * 0.02).bfloat16()
+        ms = timed(lambda: F.lora_down(x, a))
+        nbytes = 2 * M * K + 2 * r * K + 2 * M * r
+        peaks, kind = measured_peaks()
+        want = (x.float() @ a.float().t())
+        got = F.lora_down(x, a).float()
+        # the result is rounded to bf16: allow one step at the value's magnitude (2^-8 relative) on top of the RMS floor
+        err = float(((got - want).abs() / (want.abs() + want.pow(2).mean().sqrt())).max())
+        out[f"lora_down M={M} K={K} r={r}"] = {"ms": ms, "algorithmic_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                                                "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                                "max_err_over_magnitude_vs_fp32": err}
+        all_equal = all_equal and err <= 2.0 ** -8
+        launches += 20
+    status = pkg._native.device_status()
+    if dist is not None:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    head = out["lora_down M=8192 K=4096 r=64"]
+    print(json.dumps({"metric": "lora_down_bandwidth", "value": head["gbs"], "unit": "GB/s", "n_gpus": world, "steps": 20,
+                      "warmup": 3, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "sub_wave_gemms", "l2": "operands of the int8 cases are L2-resident by design (they "
+                                 "are smaller than L2 in the model too); the LoRA input (67 MB) is re-read from HBM"},
+                      "roofline": {"bound": "hbm", "kernel": "gemm_tcgen05_kernel<bf16, 64, single, K split>", "achieved": head["gbs"],
+                                   "peak": measured_peaks()[0]["hbm_gbs"], "unit": "GB/s", "frac": head["frac_of_hbm"], "traffic": None},
+                      "kernels": out, "ok": all_equal, "gpu_launches": launches, "device_status": status}))
+    if not all_equal or status != 0:
+        sys.exit(1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm", "prologue"], default="c1")
+    ap.add_argument("--workload", choices=["c0", "c1", "c2", "c2merge", "c4", "dit", "smallm", "prologue", "subwave"], default="c1")
     ap.add_argument("--no-graph", action="store_true", help="dit: run eagerly instead of replaying a CUDA graph")
     ap.add_argument("--dit-unfused", action="store_true",
                     help="dit: the block code without the fused quantiser prologues (every element-wise step a PyTorch call)")
@@ -1335,6 +1422,8 @@ def main():
         run_small_batch(args)
     elif args.workload == "prologue":
         run_prologue(args)
+    elif args.workload == "subwave":
+        run_subwave(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
