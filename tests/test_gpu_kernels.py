@@ -481,7 +481,10 @@ def test_peer_barrier_meets_and_times_out_on_one_gpu(cuda_pkg):
 
 # ------------------------------------------------------------------ quantiser prologues
 @pytest.mark.parametrize("M,K,dt", [(64, 4096, torch.bfloat16), (33, 256, torch.bfloat16), (7, 1032, torch.float16),
-                                    (130, 12288, torch.bfloat16), (5, 16384, torch.float16), (1, 8, torch.bfloat16)])
+                                    (130, 12288, torch.bfloat16), (5, 16384, torch.float16), (1, 8, torch.bfloat16),
+                                    # thousands of rows (several waves of CTAs), row counts that are no multiple of the
+                                    # rows per CTA
+                                    (2051, 4096, torch.bfloat16), (2300, 2056, torch.float16)])
 def test_ln_modulate_quantiser_bit_exact(cuda_pkg, M, K, dt):
     """LayerNorm -> (1 + scale), shift -> per-token int8 in one kernel: int8, scales and the modulated activations
     equal the bit-level definition; the same tensor built from PyTorch's own LayerNorm and addcmul agrees to within
@@ -497,6 +500,10 @@ def test_ln_modulate_quantiser_bit_exact(cuda_pkg, M, K, dt):
     assert np.array_equal(to_np(rs), s_want) and np.array_equal(to_np(q), q_want)
     q2, rs2 = F.quantize_rowwise_ln_modulate(x.to(DEV), shift.to(DEV), scale.to(DEV), eps=1e-5)
     assert torch.equal(q2, q) and torch.equal(rs2, rs)
+    wide = torch.zeros(M, K + 32, dtype=dt, device=DEV)      # a pitched input (column slice of a wider buffer)
+    wide[:, 16:16 + K] = x.to(DEV)
+    q3, rs3 = F.quantize_rowwise_ln_modulate(wide[:, 16:16 + K], shift.to(DEV), scale.to(DEV), eps=1e-5)
+    assert torch.equal(q3, q) and torch.equal(rs3, rs)
     lib = torch.addcmul(shift.to(DEV), torch.nn.functional.layer_norm(x.to(DEV), (K,)), 1 + scale.to(DEV))
     d = (y.float() - lib.float()).abs()
     # steps of the 16-bit type at the magnitude of the terms (the modulated value can be a small difference of large ones)
