@@ -515,7 +515,9 @@ def test_ln_modulate_quantiser_bit_exact(cuda_pkg, M, K, dt):
 @pytest.mark.parametrize("M,K0,K1,dt", [(64, 0, 12288, torch.bfloat16), (40, 4096, 12288, torch.bfloat16), (9, 128, 264, torch.float16),
                                         (3, 0, 8, torch.bfloat16), (130, 256, 768, torch.bfloat16),
                                         # large enough for the look-up-table kernel (persistent CTAs, four rows each)
-                                        (301, 4096, 12288, torch.bfloat16), (182, 0, 12288, torch.float16), (1027, 0, 2056, torch.bfloat16)])
+                                        (301, 4096, 12288, torch.bfloat16), (182, 0, 12288, torch.float16), (1027, 0, 2056, torch.bfloat16),
+                                        # a thousand rows and more, two sources, row counts that are no multiple of the grid
+                                        (1100, 4096, 12288, torch.bfloat16), (1500, 1024, 3080, torch.float16)])
 def test_gelu_quantiser_bit_exact(cuda_pkg, M, K0, K1, dt):
     """[ plain | GELU_tanh ] -> per-token int8 in one kernel, the two parts read as column slices of wider matrices."""
     F, wl = cuda_pkg.functional, cuda_pkg.workloads
