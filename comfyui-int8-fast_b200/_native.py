@@ -59,6 +59,8 @@ _PROTOTYPES = {
                                         ctypes.POINTER(c_void_p), c_int, c_int64, c_int64, c_int64, c_int, c_int64, c_int64,
                                         c_int64, c_int, c_void_p]),
     "i8f_launch_count": (ctypes.c_uint64, []),
+    "i8f_gemm_plan": (c_int, [c_int64, c_int64, c_int64, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                              ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
     "i8f_linear_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "i8f_linear_forward": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                    c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p,

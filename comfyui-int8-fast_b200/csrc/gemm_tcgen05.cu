@@ -1072,11 +1072,16 @@ int launch_gemm(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t 
 // Tile shape by problem shape: CTA pairs on 256 x 256 tiles when both extents
 // are large, single CTAs with 128 x {256,128,64} tiles otherwise (LoRA ranks,
 // short batches).
-template <int KIND>
-int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
-                     const GemmParams& p, cudaStream_t st, const Scatter* scatter = nullptr) {
-    // I8F_GEMM_TILE = pair256 | s256 | s128 | s64 | s32 forces one tile configuration (experiments);
-    // I8F_GEMM_SINGLE_CTA=1 is the older spelling of "never pair"
+// Tile configuration of one GEMM: 1 pair 256 x 256, 2 single 128 x 256, 3 single 128 x 128, 4 single 128 x 64,
+// 5 single 128 x 32; k_split 1 or 2 (two CTAs of a cluster share a tile's K range).
+struct GemmPlan {
+    int choice;
+    int k_split;
+};
+
+// I8F_GEMM_TILE = pair256 | s256 | s128 | s64 | s32 forces one tile configuration (experiments);
+// I8F_GEMM_SINGLE_CTA=1 is the older spelling of "never pair"; I8F_KSPLIT=0 switches the K split off.
+int forced_tile() {
     static const int forced = [] {
         const char* e = getenv("I8F_GEMM_TILE");
         if (e != nullptr) {
@@ -1089,70 +1094,83 @@ int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int
         const char* f = getenv("I8F_GEMM_SINGLE_CTA");
         return (f != nullptr && f[0] == '1') ? 5 : 0;
     }();
-    int k_split = 1;
-    int choice;   // 1 pair 256 x 256, 2 single 128 x 256, 3 single 128 x 128, 4 single 128 x 64, 5 single 128 x 32
+    return forced;
+}
+bool ksplit_enabled() {
+    static const int on = [] {
+        const char* e = getenv("I8F_KSPLIT");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return on != 0;
+}
+
+// Pure function of the shape, the SM count and the switches.  elem_bytes: 1 for int8 operands, 2 for the 16-bit kinds.
+GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int elem_bytes, int64_t sms, bool scatter, int forced, bool ksplit_on) {
+    GemmPlan plan{0, 1};
     if ((forced >= 1 && forced <= 4) || forced == 6) {
-        choice = forced == 6 ? 5 : forced;
-    } else {
-        // Problems that do not fill the GPU with 256-wide tiles are bound by how many SMs pull operands, not by the
-        // tensor pipe (one tile's K loop costs 13 - 18 us whatever its width): take the configuration with the most
-        // CTAs that still fit one wave, and among equals the one with the least padded work.  Everything larger
-        // runs the paired 256 x 256 tiles.  (Measured on M = 17 .. 2048, N = 4096 / 12288, K = 4096.)
-        const int64_t sms = sm_count();
-        const int64_t m128 = (M + 127) / 128, m256 = (M + 255) / 256;
-        const int64_t ctas[6] = {0, 2 * m256 * ((N + 255) / 256), m128 * ((N + 255) / 256), m128 * ((N + 127) / 128),
-                                 m128 * ((N + 63) / 64), m128 * ((N + 31) / 32)};
-        const int64_t work[6] = {0, m256 * 256 * ((N + 255) / 256) * 256, m128 * 128 * ((N + 255) / 256) * 256,
-                                 m128 * 128 * ((N + 127) / 128) * 128, m128 * 128 * ((N + 63) / 64) * 64,
-                                 m128 * 128 * ((N + 31) / 32) * 32};
-        choice = 0;
+        plan.choice = forced == 6 ? 5 : forced;
+        return plan;
+    }
+    // Problems that do not fill the GPU with 256-wide tiles are bound by how many SMs work on them (one tile's K loop
+    // costs the same whatever its width): take the configuration with the most CTAs that still fit one wave, and among
+    // equals the one with the least padded work.  Everything larger runs the paired 256 x 256 tiles.  (Measured on
+    // M = 17 .. 2048, N = 4096 / 12288, K = 4096.)
+    const int64_t m128 = (M + 127) / 128, m256 = (M + 255) / 256;
+    const int64_t ctas[6] = {0, 2 * m256 * ((N + 255) / 256), m128 * ((N + 255) / 256), m128 * ((N + 127) / 128),
+                             m128 * ((N + 63) / 64), m128 * ((N + 31) / 32)};
+    const int64_t work[6] = {0, m256 * 256 * ((N + 255) / 256) * 256, m128 * 128 * ((N + 255) / 256) * 256,
+                             m128 * 128 * ((N + 127) / 128) * 128, m128 * 128 * ((N + 63) / 64) * 64,
+                             m128 * 128 * ((N + 31) / 32) * 32};
+    int choice = 0;
+    for (int c = 1; c <= 5; ++c) {
+        if (c == 1 && forced == 5) continue;
+        if (c == 5 && scatter) continue;   // the scatter epilogue stores 64-column pieces
+        if (ctas[c] > sms) continue;
+        if (choice == 0 || ctas[c] > ctas[choice] || (ctas[c] == ctas[choice] && work[c] < work[choice])) choice = c;
+    }
+    if (choice == 0) choice = N > 128 ? ((M > 128 && forced != 5) ? 1 : 2) : (N > 64 ? 3 : 4);
+    plan.choice = choice;
+    // K split: when a single-CTA configuration leaves at least half of the SMs without a tile, two CTAs may share
+    // each tile's K range.  Estimated cycles of one CTA, fitted to measurements on M = 17 .. 512, K = 3072 .. 12288:
+    // K slabs x max(560 issue-and-tensor cycles, operand bytes at 72 B/clk), 1100 per 32-column chunk of the epilogue,
+    // 3700 + 950 per chunk for the hand-over.  The split is taken when its best candidate is at least 7 % cheaper than
+    // the best unsplit one.
+    if (ksplit_on && !scatter && forced == 0) {
+        const int64_t nkb = (K * elem_bytes + kStageRowBytes - 1) / kStageRowBytes;
+        const int bn_of[6] = {0, 256, 256, 128, 64, 32};
+        auto est = [&](int c, int split) -> int64_t {
+            const int64_t chunks = bn_of[c] / 32;
+            const int64_t slab_bytes = (c == 1 ? 16384 + 128 * 128 : 16384 + bn_of[c] * 128);
+            const int64_t slab = slab_bytes / 72 > 560 ? slab_bytes / 72 : 560;
+            return (nkb / split) * slab + chunks * 1100 + (split == 2 ? 3700 + chunks * 950 : 0);
+        };
+        int64_t best[3] = {0, -1, -1};
+        int best_c = 0;
         for (int c = 1; c <= 5; ++c) {
-            if (c == 1 && forced == 5) continue;
-            if (c == 5 && scatter != nullptr) continue;   // the scatter epilogue stores 64-column pieces
             if (ctas[c] > sms) continue;
-            if (choice == 0 || ctas[c] > ctas[choice] || (ctas[c] == ctas[choice] && work[c] < work[choice])) choice = c;
-        }
-        if (choice == 0) choice = N > 128 ? ((M > 128 && forced != 5) ? 1 : 2) : (N > 64 ? 3 : 4);
-        // K split: when a single-CTA configuration leaves at least half of the SMs without a tile, two CTAs may share
-        // each tile's K range.  Estimated cycles of one CTA, fitted to measurements on M = 17 .. 512, K = 3072 .. 12288:
-        // K slabs x max(560 issue-and-tensor cycles, operand bytes at 72 B/clk), 1100 per 32-column chunk of the epilogue,
-        // 3700 + 950 per chunk for the hand-over.  The split is taken when its best candidate is at least 7 % cheaper than
-        // the best unsplit one (I8F_KSPLIT=0 switches it off).
-        static const int ksplit_on = [] {
-            const char* e = getenv("I8F_KSPLIT");
-            return (e != nullptr && e[0] == '0') ? 0 : 1;
-        }();
-        if (ksplit_on && scatter == nullptr && forced == 0) {
-            const int esz = KIND == kKindI8 ? 1 : 2;
-            const int64_t nkb = (K * esz + kStageRowBytes - 1) / kStageRowBytes;
-            const int bn_of[6] = {0, 256, 256, 128, 64, 32};
-            auto est = [&](int c, int split) -> int64_t {
-                const int64_t chunks = bn_of[c] / 32;
-                const int64_t slab_bytes = (c == 1 ? 16384 + 128 * 128 : 16384 + bn_of[c] * 128);
-                const int64_t slab = slab_bytes / 72 > 560 ? slab_bytes / 72 : 560;
-                return (nkb / split) * slab + chunks * 1100 + (split == 2 ? 3700 + chunks * 950 : 0);
-            };
-            int64_t best[3] = {0, -1, -1};
-            int best_c = 0;
-            for (int c = 1; c <= 5; ++c) {
-                if (ctas[c] > sms) continue;
-                for (int split = 1; split <= 2; ++split) {
-                    if (split == 2 && (c == 1 || 2 * ctas[c] > sms || nkb < 8)) continue;
-                    const int64_t e = est(c, split);
-                    if (best[split] < 0 || e < best[split]) {
-                        best[split] = e;
-                        if (split == 2) best_c = c;
-                    }
+            for (int split = 1; split <= 2; ++split) {
+                if (split == 2 && (c == 1 || 2 * ctas[c] > sms || nkb < 8)) continue;
+                const int64_t e = est(c, split);
+                if (best[split] < 0 || e < best[split]) {
+                    best[split] = e;
+                    if (split == 2) best_c = c;
                 }
             }
-            const int best_split = (best[2] >= 0 && best[1] >= 0 && best[2] * 100 < best[1] * 93) ? 2 : 1;
-            if (best_c != 0 && best_split == 2) {
-                choice = best_c;
-                k_split = 2;
-            }
+        }
+        if (best_c != 0 && best[2] >= 0 && best[1] >= 0 && best[2] * 100 < best[1] * 93) {
+            plan.choice = best_c;
+            plan.k_split = 2;
         }
     }
-    switch (choice) {
+    return plan;
+}
+
+template <int KIND>
+int launch_gemm_auto(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t M, int64_t N, int64_t K,
+                     const GemmParams& p, cudaStream_t st, const Scatter* scatter = nullptr) {
+    const GemmPlan plan = plan_gemm(M, N, K, KIND == kKindI8 ? 1 : 2, sm_count(), scatter != nullptr, forced_tile(), ksplit_enabled());
+    const int k_split = plan.k_split;
+    switch (plan.choice) {
         case 1: return launch_gemm<KIND, 256, true>(a, lda, b, ldb, M, N, K, p, st, scatter);
         case 2: return launch_gemm<KIND, 256, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
         case 3: return launch_gemm<KIND, 128, false>(a, lda, b, ldb, M, N, K, p, st, scatter, nullptr, k_split);
@@ -1181,6 +1199,20 @@ int check_operands(const void* a, int64_t lda, const void* b, int64_t ldb, int e
 using namespace i8f;
 
 extern "C" {
+
+int i8f_gemm_plan(int64_t M, int64_t N, int64_t K, int elem_bytes, int sm_count_or_0, int* tile_rows, int* tile_cols,
+                  int* ctas_per_tile, int* k_split) {
+    I8F_REQUIRE(M > 0 && N > 0 && K > 0 && (elem_bytes == 1 || elem_bytes == 2), I8F_ERR_INVALID_ARG, "bad shape or element size");
+    I8F_REQUIRE(tile_rows != nullptr && tile_cols != nullptr && ctas_per_tile != nullptr && k_split != nullptr, I8F_ERR_INVALID_ARG,
+                "NULL output pointer");
+    const GemmPlan plan = plan_gemm(M, N, K, elem_bytes, sm_count_or_0 > 0 ? sm_count_or_0 : sm_count(), false, 0, true);
+    const int rows_of[6] = {0, 256, 128, 128, 128, 128}, cols_of[6] = {0, 256, 256, 128, 64, 32};
+    *tile_rows = rows_of[plan.choice];
+    *tile_cols = cols_of[plan.choice];
+    *k_split = plan.k_split;
+    *ctas_per_tile = (plan.choice == 1 ? 2 : 1) * plan.k_split;
+    return I8F_OK;
+}
 
 int i8f_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
     I8F_REQUIRE(limit_cycles > 0 && limit_cycles <= 4000000000LL, I8F_ERR_INVALID_ARG, "limit_cycles out of range");

@@ -445,6 +445,15 @@ def lora_merge_sr_(w: Tensor, w_scale, up: Tensor, down: Tensor, lora_scale: flo
     return w
 
 
+def gemm_plan(M: int, N: int, K: int, elem_bytes: int = 1, sm_count: int = 0) -> dict:
+    """The tile configuration the GEMM entry points choose for this shape (host-side decision, no device needed):
+    {'tile': (rows, cols), 'ctas_per_tile': n, 'k_split': 1 | 2}."""
+    import ctypes
+    out = [ctypes.c_int(0) for _ in range(4)]
+    nat.check(nat.load().i8f_gemm_plan(M, N, K, elem_bytes, sm_count, *[ctypes.byref(o) for o in out]), "i8f_gemm_plan")
+    return {"tile": (out[0].value, out[1].value), "ctas_per_tile": out[2].value, "k_split": out[3].value}
+
+
 def lora_merge_max_rank(factor_dtype: torch.dtype, with_uniforms: bool = False) -> int:
     """Largest rank the fused merge kernel takes in one launch for factors of this dtype."""
     return int(nat.load().i8f_lora_merge_max_rank(_code(factor_dtype), 1 if with_uniforms else 0))

@@ -73,6 +73,15 @@ int i8f_device_check(void);
  * Synchronises the device; meant for tests and diagnostics. */
 int i8f_device_status(int* status_out, int reset);
 
+/* Diagnostic, host only (no device needed): the tile configuration the GEMM entry points choose for an
+ * [M,K] x [N,K]^T problem with 1-byte (int8) or 2-byte (bf16 / fp16) operands on a GPU with `sm_count_or_0` SMs
+ * (0: the current device, 148 if there is none), ignoring the environment switches: tile_rows x tile_cols,
+ * ctas_per_tile (2 for the 256 x 256 tile of a CTA pair; doubled again when two CTAs of a cluster split the tile's K
+ * range) and k_split (1 or 2).  No counterpart in the reference, whose Triton kernels leave this to the autotuner
+ * (int8_fused_kernel.py:81-89). */
+int i8f_gemm_plan(int64_t M, int64_t N, int64_t K, int elem_bytes, int sm_count_or_0, int* tile_rows, int* tile_cols,
+                  int* ctas_per_tile, int* k_split);
+
 /* Diagnostic: launches one CTA that waits on a barrier nothing signals.  The device-side wait gives up after
  * `limit_cycles` SM clocks, the kernel ends normally and i8f_device_status() then reads 199.  This is how the
  * time-out path of every in-kernel wait is exercised without hanging or faulting the GPU.  No counterpart in

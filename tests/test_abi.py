@@ -57,6 +57,31 @@ def test_argument_errors_are_reported_not_raised_as_faults(pkg):
     assert lib.i8f_linear_workspace_bytes(4, 64) == 256 + 256
 
 
+def test_gemm_tile_plan_is_a_host_decision_and_pinned(pkg):
+    """Which tiles a GEMM runs on, and whether two CTAs of a cluster split a tile's K range, is decided on the host
+    from the shape and the SM count alone: pinned here for the benchmark shapes on 148 SMs."""
+    plan = pkg.functional.gemm_plan
+    # the headline linear and the DiT's image-stream linears: full-rate 256 x 256 tiles of a CTA pair, never split
+    assert plan(4096, 12288, 4096, sm_count=148) == {"tile": (256, 256), "ctas_per_tile": 2, "k_split": 1}
+    assert plan(4608, 24576, 4096, sm_count=148)["tile"] == (256, 256)
+    # configuration 0 of the baseline (96 CTAs of 128 x 64 fill most of the GPU: the split would not pay)
+    assert plan(256, 3072, 3072, sm_count=148) == {"tile": (128, 64), "ctas_per_tile": 1, "k_split": 1}
+    # the DiT's text-stream linears at K = 4096: 128 CTAs already
+    assert plan(512, 4096, 4096, sm_count=148) == {"tile": (128, 128), "ctas_per_tile": 1, "k_split": 1}
+    # few tiles and a long K: two CTAs per tile
+    assert plan(64, 4096, 4096, sm_count=148) == {"tile": (128, 64), "ctas_per_tile": 2, "k_split": 2}
+    assert plan(17, 4096, 4096, sm_count=148)["k_split"] == 2
+    assert plan(512, 4096, 12288, sm_count=148) == {"tile": (128, 256), "ctas_per_tile": 2, "k_split": 2}
+    # the LoRA down projection (16-bit operands, N = rank): 64 tiles -> 128 CTAs
+    assert plan(8192, 64, 4096, elem_bytes=2, sm_count=148) == {"tile": (128, 64), "ctas_per_tile": 2, "k_split": 2}
+    assert plan(4608, 16, 4096, elem_bytes=2, sm_count=148) == {"tile": (128, 32), "ctas_per_tile": 2, "k_split": 2}
+    # a short K never splits; a smaller GPU changes the decision
+    assert plan(64, 4096, 512, sm_count=148)["k_split"] == 1
+    assert plan(64, 4096, 4096, sm_count=64)["k_split"] == 1
+    with pytest.raises(pkg._native.NativeLibraryError):
+        plan(0, 64, 64)
+
+
 def test_cpu_tensors_are_rejected(pkg):
     import torch
     with pytest.raises(pkg._native.NativeLibraryError, match="CUDA"):
