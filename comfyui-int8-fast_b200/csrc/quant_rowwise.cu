@@ -301,7 +301,7 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
     // this grid has started; it still waits for this grid to complete before it reads anything
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int tpr = 1 << tpr_log2;
-    const int rows_per_cta = kThreads >> tpr_log2;
+    const int rows_per_cta = static_cast<int>(blockDim.x) >> tpr_log2;
     const int t = threadIdx.x & (tpr - 1);
     const int lane = threadIdx.x & 31;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_cta + (threadIdx.x >> tpr_log2);
@@ -444,7 +444,7 @@ quant_rows_kernel(const void* __restrict__ x, int64_t M, int64_t K, int64_t ldx,
             if constexpr (MODE == kAbsmaxOnly) {
                 if (threadIdx.x == 0) {
                     float m = 0.f;
-                    for (int w = 0; w < kThreads / 32; ++w) m = fmaxf(m, s_part[w]);
+                    for (int w = 0; w < static_cast<int>(blockDim.x) / 32; ++w) m = fmaxf(m, s_part[w]);
                     // non-negative floats order like their bit patterns
                     atomicMax(reinterpret_cast<int*>(gmax), __float_as_int(m));
                 }
@@ -508,10 +508,17 @@ inline bool make_plan(int64_t K, Plan* p) {
 template <int DT, bool HAD, bool ROT_F32, int MODE>
 int launch_vpt(const Plan& p, const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, int64_t ldq, float* scale,
                void* xrot, float* gmax, cudaStream_t st) {
-    const int rows_per_cta = kThreads >> p.tpr_log2;
+    // CTA size: 128 threads where a row needs no more (finer-grained CTAs: 14.6 -> 14.3 us with rotation and
+    // 10.3 -> 10.0 us without at 4096 x 4096), else 256; I8F_K1_THREADS=256 forces the larger one
+    static const int want_threads = [] {
+        const char* e = getenv("I8F_K1_THREADS");
+        return (e != nullptr && atoi(e) == 256) ? 256 : 128;
+    }();
+    const int threads = (want_threads == 128 && p.tpr_log2 <= 7) ? 128 : kThreads;
+    const int rows_per_cta = threads >> p.tpr_log2;
     const unsigned grid = static_cast<unsigned>((M + rows_per_cta - 1) / rows_per_cta);
 #define I8F_LAUNCH(V)                                                                                              \
-    quant_rows_kernel<DT, V, HAD, ROT_F32, MODE><<<grid, kThreads, 0, st>>>(x, M, K, ldx, q, ldq, scale, xrot, gmax, \
+    quant_rows_kernel<DT, V, HAD, ROT_F32, MODE><<<grid, threads, 0, st>>>(x, M, K, ldx, q, ldq, scale, xrot, gmax, \
                                                                             p.tpr_log2)
     switch (p.vpt) {
         case 1: I8F_LAUNCH(1); break;
